@@ -1,0 +1,618 @@
+// libb200moe.so - host side of the C ABI declared in include/b200moe.h: argument checks,
+// workspace, expert pointer tables and kernel launches.  No torch types, no CPU compute path.
+#include "../../include/b200moe.h"
+
+#include <cuda_runtime.h>
+
+#include <cstdarg>
+#include <cstdio>
+#include <cstring>
+#include <new>
+#include <string>
+#include <vector>
+
+#include "common.cuh"
+#include "ffn_gemv.cuh"
+#include "int4_pack.cuh"
+#include "permute.cuh"
+#include "router.cuh"
+#ifdef B200MOE_WITH_INT4
+#include "ffn_int4.cuh"
+#endif
+#ifdef B200MOE_WITH_UMMA
+#include "ffn_umma.cuh"
+#endif
+
+using namespace b200moe;
+
+struct b200moe_ctx {
+  b200moe_config cfg{};
+  int sm_count = 0;
+  std::string err;
+  int64_t launches = 0;
+  // registered weights (host mirror) and the device table
+  std::vector<const void*> gate_w, gate_bias;
+  std::vector<ExpertPtrs> h_experts;
+  std::vector<uint8_t> registered;
+  std::vector<uint8_t> dirty;
+  ExpertPtrs* d_experts = nullptr;  // [L*E (+1 scratch entry for expert_ffn)]
+  float* wnorm2 = nullptr;          // [L*E]
+  // workspace
+  float* logit_sum = nullptr;
+  float* xnorm2 = nullptr;
+  unsigned* tile_counter = nullptr;
+  int64_t* ids64 = nullptr;
+  void* scores = nullptr;
+  int* offsets = nullptr;
+  int* sorted_pair = nullptr;
+  int* inv = nullptr;
+  int* act_list = nullptr;
+  int* n_act = nullptr;
+  void* h = nullptr;
+  void* y = nullptr;
+  int* status = nullptr;
+  unsigned long long* bitmap = nullptr;
+  // second, tiny table set used by b200moe_expert_ffn (one expert, identity permutation)
+  int* one_offsets = nullptr;
+  int* one_sorted = nullptr;
+  int* one_act = nullptr;
+  int* one_nact = nullptr;
+  std::vector<void*> allocs;
+  // optional per-kernel timing (b200moe_profile): one event pair per launch, grouped by kernel class
+  bool profiling = false;
+  struct ProfRec { int cls; cudaEvent_t a, b; };
+  std::vector<ProfRec> prof;
+};
+
+// Brackets one kernel launch with CUDA events on the launching stream while profiling is on.
+struct ProfScope {
+  b200moe_ctx* ctx; cudaStream_t st; int idx = -1;
+  ProfScope(b200moe_ctx* c, int cls, cudaStream_t s) : ctx(c), st(s) {
+    if (!c || !c->profiling) return;
+    b200moe_ctx::ProfRec r{cls, nullptr, nullptr};
+    if (cudaEventCreate(&r.a) != cudaSuccess || cudaEventCreate(&r.b) != cudaSuccess) return;
+    cudaEventRecord(r.a, s);
+    c->prof.push_back(r);
+    idx = (int)c->prof.size() - 1;
+  }
+  ~ProfScope() { if (idx >= 0) cudaEventRecord(ctx->prof[idx].b, st); }
+};
+
+static thread_local std::string g_err;
+
+static int fail(b200moe_ctx* ctx, int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
+  if (ctx) ctx->err = buf;
+  g_err = buf;
+  return code;
+}
+
+#define CUDA_TRY(ctx, call)                                                                        \
+  do {                                                                                             \
+    cudaError_t e_ = (call);                                                                       \
+    if (e_ != cudaSuccess)                                                                         \
+      return fail(ctx, B200MOE_E_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
+  } while (0)
+
+static size_t elem_bytes(int dtype) { return dtype == B200MOE_F32 ? 4 : 2; }
+
+template <typename T> static int dev_alloc(b200moe_ctx* ctx, T** p, size_t count) {
+  void* q = nullptr;
+  cudaError_t e = cudaMalloc(&q, count * sizeof(T) > 0 ? count * sizeof(T) : 16);
+  if (e != cudaSuccess) return fail(ctx, B200MOE_E_CUDA, "cudaMalloc(%zu bytes) failed: %s", count * sizeof(T), cudaGetErrorString(e));
+  ctx->allocs.push_back(q);
+  *p = reinterpret_cast<T*>(q);
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_abi_version(void) { return 1; }
+
+extern "C" const char* b200moe_last_error(const b200moe_ctx* ctx) { return ctx ? ctx->err.c_str() : g_err.c_str(); }
+
+extern "C" int64_t b200moe_launch_count(const b200moe_ctx* ctx) { return ctx ? ctx->launches : 0; }
+
+extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
+  if (!cfg || !out) return fail(nullptr, B200MOE_E_ARG, "b200moe_create: null argument");
+  *out = nullptr;
+  const int H = cfg->hidden_size, E = cfg->num_experts, K = cfg->top_k, I = cfg->intermediate_size;
+  if (H <= 0 || I <= 0 || E <= 0 || K <= 0 || cfg->num_layers <= 0 || cfg->max_tokens <= 0)
+    return fail(nullptr, B200MOE_E_ARG, "b200moe_create: sizes must be positive");
+  if (E > B200MOE_MAX_EXPERTS) return fail(nullptr, B200MOE_E_UNSUPPORTED, "num_experts %d > %d", E, B200MOE_MAX_EXPERTS);
+  if (K > E || K > B200MOE_MAX_TOPK) return fail(nullptr, B200MOE_E_ARG, "top_k %d must be <= min(num_experts, %d)", K, B200MOE_MAX_TOPK);
+  if (cfg->act_dtype < B200MOE_F32 || cfg->act_dtype > B200MOE_BF16) return fail(nullptr, B200MOE_E_ARG, "unknown act_dtype %d", cfg->act_dtype);
+  if (cfg->weight_mode != B200MOE_W_DENSE && cfg->weight_mode != B200MOE_W_INT4_G128)
+    return fail(nullptr, B200MOE_E_ARG, "unknown weight_mode %d", cfg->weight_mode);
+  const int mult = cfg->weight_mode == B200MOE_W_INT4_G128 ? 128 : 8;
+  if (H % mult || I % mult) return fail(nullptr, B200MOE_E_ARG, "hidden_size and intermediate_size must be multiples of %d", mult);
+  if (cfg->weight_mode == B200MOE_W_INT4_G128 && cfg->act_dtype != B200MOE_BF16)
+    return fail(nullptr, B200MOE_E_UNSUPPORTED, "int4 expert weights need bf16 activations");
+#ifndef B200MOE_WITH_INT4
+  if (cfg->weight_mode == B200MOE_W_INT4_G128) return fail(nullptr, B200MOE_E_UNSUPPORTED, "library built without the int4 kernels");
+#endif
+  int ndev = 0;
+  cudaError_t e = cudaGetDeviceCount(&ndev);
+  if (e != cudaSuccess || ndev == 0)
+    return fail(nullptr, B200MOE_E_CUDA, "no CUDA device: %s (this library has no CPU path)", cudaGetErrorString(e));
+  if (cfg->device < 0 || cfg->device >= ndev) return fail(nullptr, B200MOE_E_ARG, "device %d out of range", cfg->device);
+  CUDA_TRY(nullptr, cudaSetDevice(cfg->device));
+  cudaDeviceProp prop;
+  CUDA_TRY(nullptr, cudaGetDeviceProperties(&prop, cfg->device));
+  if (prop.major != 10) return fail(nullptr, B200MOE_E_UNSUPPORTED, "device is sm_%d%d; this library is built for sm_100a only", prop.major, prop.minor);
+
+  b200moe_ctx* ctx = new (std::nothrow) b200moe_ctx();
+  if (!ctx) return fail(nullptr, B200MOE_E_CUDA, "out of host memory");
+  ctx->cfg = *cfg;
+  ctx->sm_count = prop.multiProcessorCount;
+  const size_t L = cfg->num_layers, Tm = cfg->max_tokens, eb = elem_bytes(cfg->act_dtype);
+  ctx->gate_w.assign(L, nullptr);
+  ctx->gate_bias.assign(L, nullptr);
+  ctx->h_experts.assign(L * E, ExpertPtrs{});
+  ctx->registered.assign(L * E, 0);
+  ctx->dirty.assign(L, 0);
+  int rc = B200MOE_OK;
+  char* hb = nullptr;
+  char* yb = nullptr;
+  char* sb = nullptr;
+  const size_t pairs = Tm * K;
+  if ((rc = dev_alloc(ctx, &ctx->d_experts, L * E + 1)) || (rc = dev_alloc(ctx, &ctx->wnorm2, L * E)) ||
+      (rc = dev_alloc(ctx, &ctx->logit_sum, Tm * E)) || (rc = dev_alloc(ctx, &ctx->xnorm2, Tm)) ||
+      (rc = dev_alloc(ctx, &ctx->tile_counter, Tm)) || (rc = dev_alloc(ctx, &ctx->ids64, pairs)) ||
+      (rc = dev_alloc(ctx, &sb, pairs * 4)) || (rc = dev_alloc(ctx, &ctx->offsets, (size_t)E + 1)) ||
+      (rc = dev_alloc(ctx, &ctx->sorted_pair, pairs)) || (rc = dev_alloc(ctx, &ctx->inv, pairs)) ||
+      (rc = dev_alloc(ctx, &ctx->act_list, (size_t)E)) || (rc = dev_alloc(ctx, &ctx->n_act, 4)) ||
+      (rc = dev_alloc(ctx, &hb, pairs * I * eb)) || (rc = dev_alloc(ctx, &yb, pairs * H * eb)) ||
+      (rc = dev_alloc(ctx, &ctx->status, 4)) || (rc = dev_alloc(ctx, &ctx->bitmap, 4)) ||
+      (rc = dev_alloc(ctx, &ctx->one_offsets, 2)) || (rc = dev_alloc(ctx, &ctx->one_sorted, pairs)) ||
+      (rc = dev_alloc(ctx, &ctx->one_act, 1)) || (rc = dev_alloc(ctx, &ctx->one_nact, 1))) {
+    std::string msg = ctx->err;
+    b200moe_destroy(ctx);
+    return fail(nullptr, rc, "%s", msg.c_str());
+  }
+  ctx->h = hb;
+  ctx->y = yb;
+  ctx->scores = sb;
+  cudaMemset(ctx->tile_counter, 0, Tm * sizeof(unsigned));
+  cudaMemset(ctx->status, 0, sizeof(int));
+  cudaMemset(ctx->d_experts, 0, (L * E + 1) * sizeof(ExpertPtrs));
+  {
+    std::vector<int> iota(pairs);
+    for (size_t i = 0; i < pairs; ++i) iota[i] = (int)i;
+    cudaMemcpy(ctx->one_sorted, iota.data(), pairs * sizeof(int), cudaMemcpyHostToDevice);
+    const int zero_one[2] = {0, 1};
+    cudaMemcpy(ctx->one_act, &zero_one[0], sizeof(int), cudaMemcpyHostToDevice);
+    cudaMemcpy(ctx->one_nact, &zero_one[1], sizeof(int), cudaMemcpyHostToDevice);
+  }
+  e = cudaDeviceSynchronize();
+  if (e != cudaSuccess) {
+    b200moe_destroy(ctx);
+    return fail(nullptr, B200MOE_E_CUDA, "workspace initialisation failed: %s", cudaGetErrorString(e));
+  }
+  *out = ctx;
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_destroy(b200moe_ctx* ctx) {
+  if (!ctx) return B200MOE_OK;
+  cudaSetDevice(ctx->cfg.device);
+  for (auto& r : ctx->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  for (void* p : ctx->allocs) cudaFree(p);
+  delete ctx;
+  return B200MOE_OK;
+}
+
+static int check_layer(b200moe_ctx* ctx, int layer, const char* who) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "%s: null context", who);
+  if (layer < 0 || layer >= ctx->cfg.num_layers) return fail(ctx, B200MOE_E_ARG, "%s: layer %d out of range [0,%d)", who, layer, ctx->cfg.num_layers);
+  return B200MOE_OK;
+}
+static int check_tokens(b200moe_ctx* ctx, int T, const char* who) {
+  if (T < 0) return fail(ctx, B200MOE_E_ARG, "%s: negative token count", who);
+  if (T > ctx->cfg.max_tokens) return fail(ctx, B200MOE_E_STATE, "%s: T=%d exceeds the context's max_tokens=%d", who, T, ctx->cfg.max_tokens);
+  return B200MOE_OK;
+}
+static bool misaligned(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) != 0; }
+
+template <typename F> static int dispatch_dtype(b200moe_ctx* ctx, int dtype, F&& f) {
+  switch (dtype) {
+    case B200MOE_F32: return f(float{});
+    case B200MOE_F16: return f(__half{});
+    case B200MOE_BF16: return f(__nv_bfloat16{});
+  }
+  return fail(ctx, B200MOE_E_ARG, "unknown dtype %d", dtype);
+}
+
+static int post_launch(b200moe_ctx* ctx, const char* what) {
+  cudaError_t e = cudaGetLastError();
+  if (e != cudaSuccess) return fail(ctx, B200MOE_E_CUDA, "launch of %s failed: %s", what, cudaGetErrorString(e));
+  if (ctx) ctx->launches++;
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_set_gate(b200moe_ctx* ctx, int layer, const void* gate_weight, const void* bias_or_null, void* stream) {
+  int rc = check_layer(ctx, layer, "b200moe_set_gate");
+  if (rc) return rc;
+  if (!gate_weight || misaligned(gate_weight)) return fail(ctx, B200MOE_E_ARG, "b200moe_set_gate: gate weight must be a 16-byte aligned device pointer");
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  ctx->gate_w[layer] = gate_weight;
+  ctx->gate_bias[layer] = bias_or_null;
+  const int E = ctx->cfg.num_experts, H = ctx->cfg.hidden_size;
+  float* wn = ctx->wnorm2 + (size_t)layer * E;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return dispatch_dtype(ctx, ctx->cfg.act_dtype, [&](auto tag) {
+    using T = decltype(tag);
+    gate_norm_kernel<T><<<(E * 32 + 255) / 256, 256, 0, st>>>(reinterpret_cast<const T*>(gate_weight), wn, E, H);
+    return post_launch(ctx, "gate_norm_kernel");
+  });
+}
+
+extern "C" int b200moe_set_expert(b200moe_ctx* ctx, int layer, int expert, const void* gate_proj, const void* up_proj,
+                                  const void* down_proj, const void* gate_scales, const void* up_scales,
+                                  const void* down_scales) {
+  int rc = check_layer(ctx, layer, "b200moe_set_expert");
+  if (rc) return rc;
+  const int E = ctx->cfg.num_experts;
+  if (expert < 0 || expert >= E) return fail(ctx, B200MOE_E_ARG, "b200moe_set_expert: expert %d out of range [0,%d)", expert, E);
+  if (!gate_proj || !up_proj || !down_proj) return fail(ctx, B200MOE_E_ARG, "b200moe_set_expert: null weight pointer");
+  if (misaligned(gate_proj) || misaligned(up_proj) || misaligned(down_proj))
+    return fail(ctx, B200MOE_E_ARG, "b200moe_set_expert: weight pointers must be 16-byte aligned");
+  const bool int4 = ctx->cfg.weight_mode == B200MOE_W_INT4_G128;
+  if (int4 && (!gate_scales || !up_scales || !down_scales)) return fail(ctx, B200MOE_E_ARG, "b200moe_set_expert: int4 mode needs the three scale pointers");
+  if (!int4 && (gate_scales || up_scales || down_scales)) return fail(ctx, B200MOE_E_ARG, "b200moe_set_expert: scales given but the context holds dense weights");
+  if (int4 && (misaligned(gate_scales) || misaligned(up_scales) || misaligned(down_scales)))
+    return fail(ctx, B200MOE_E_ARG, "b200moe_set_expert: scale pointers must be 16-byte aligned");
+  ExpertPtrs& ep = ctx->h_experts[(size_t)layer * E + expert];
+  ep.w[0] = gate_proj; ep.w[1] = up_proj; ep.w[2] = down_proj;
+  ep.s[0] = gate_scales; ep.s[1] = up_scales; ep.s[2] = down_scales;
+  ctx->registered[(size_t)layer * E + expert] = 1;
+  ctx->dirty[layer] = 1;
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_clear_expert(b200moe_ctx* ctx, int layer, int expert) {
+  int rc = check_layer(ctx, layer, "b200moe_clear_expert");
+  if (rc) return rc;
+  const int E = ctx->cfg.num_experts;
+  if (expert < 0 || expert >= E) return fail(ctx, B200MOE_E_ARG, "b200moe_clear_expert: expert %d out of range", expert);
+  ctx->h_experts[(size_t)layer * E + expert] = ExpertPtrs{};
+  ctx->registered[(size_t)layer * E + expert] = 0;
+  ctx->dirty[layer] = 1;
+  return B200MOE_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// router
+// ------------------------------------------------------------------------------------------
+static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void* logits, int T, int64_t* ids_out,
+                         void* scores_out, unsigned long long* bitmap_dev, cudaStream_t st) {
+  const b200moe_config& c = ctx->cfg;
+  RouterParams p{};
+  p.x = x;
+  p.logits_in = logits;
+  if (!logits) {
+    p.wg = ctx->gate_w[layer];
+    p.bias = ctx->gate_bias[layer];
+    p.wnorm2 = ctx->wnorm2 + (size_t)layer * c.num_experts;
+  }
+  p.logit_sum = ctx->logit_sum;
+  p.xnorm2 = ctx->xnorm2;
+  p.tile_counter = ctx->tile_counter;
+  p.ids64 = ids_out;
+  p.scores = scores_out;
+  p.bitmap = bitmap_dev;
+  p.T = T; p.H = c.hidden_size; p.E = c.num_experts; p.K = c.top_k;
+  return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
+    using Tt = decltype(tag);
+    ProfScope prof(ctx, B200MOE_KERNEL_ROUTER, st);
+    if (logits) {
+      router_from_logits_kernel<Tt><<<(T + 7) / 8, kRouterThreads, 0, st>>>(p);
+      return post_launch(ctx, "router_from_logits_kernel");
+    }
+    dim3 grid((T + kRouterTokensPerTile - 1) / kRouterTokensPerTile, (c.num_experts + 7) / 8);
+    router_kernel<Tt><<<grid, kRouterThreads, 0, st>>>(p);
+    return post_launch(ctx, "router_kernel");
+  });
+}
+
+static int route_common(b200moe_ctx* ctx, int layer, const void* x, const void* logits, int T, int64_t* ids_out,
+                        void* scores_out, uint64_t* bitmap_out, void* stream, const char* who) {
+  int rc = check_layer(ctx, layer, who);
+  if (rc) return rc;
+  if ((rc = check_tokens(ctx, T, who))) return rc;
+  if (!ids_out || !scores_out || (!x && !logits)) return fail(ctx, B200MOE_E_ARG, "%s: null pointer", who);
+  if (!logits && !ctx->gate_w[layer]) return fail(ctx, B200MOE_E_STATE, "%s: no gate weight registered for layer %d", who, layer);
+  if (x && misaligned(x)) return fail(ctx, B200MOE_E_ARG, "%s: x must be 16-byte aligned", who);
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (T == 0) {
+    if (bitmap_out) CUDA_TRY(ctx, cudaMemsetAsync(ctx->bitmap, 0, 32, st));
+  } else {
+    if (bitmap_out) CUDA_TRY(ctx, cudaMemsetAsync(ctx->bitmap, 0, 32, st));
+    rc = launch_router(ctx, layer, x, logits, T, ids_out, scores_out, bitmap_out ? ctx->bitmap : nullptr, st);
+    if (rc) return rc;
+  }
+  if (bitmap_out) CUDA_TRY(ctx, cudaMemcpyAsync(bitmap_out, ctx->bitmap, 32, cudaMemcpyDefault, st));
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_route(b200moe_ctx* ctx, int layer, const void* x, int T, int64_t* ids_out, void* scores_out,
+                             uint64_t* active_bitmap_out, void* stream) {
+  if (!x) return fail(ctx, B200MOE_E_ARG, "b200moe_route: null x");
+  return route_common(ctx, layer, x, nullptr, T, ids_out, scores_out, active_bitmap_out, stream, "b200moe_route");
+}
+
+extern "C" int b200moe_route_from_logits(b200moe_ctx* ctx, const void* logits, int T, int64_t* ids_out, void* scores_out,
+                                         uint64_t* active_bitmap_out, void* stream) {
+  if (!logits) return fail(ctx, B200MOE_E_ARG, "b200moe_route_from_logits: null logits");
+  return route_common(ctx, 0, nullptr, logits, T, ids_out, scores_out, active_bitmap_out, stream, "b200moe_route_from_logits");
+}
+
+extern "C" int b200moe_last_logits(b200moe_ctx* ctx, int T, float* logits_out, void* stream) {
+  if (!ctx || !logits_out) return fail(ctx, B200MOE_E_ARG, "b200moe_last_logits: null argument");
+  int rc = check_tokens(ctx, T, "b200moe_last_logits");
+  if (rc) return rc;
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  CUDA_TRY(ctx, cudaMemcpyAsync(logits_out, ctx->logit_sum, (size_t)T * ctx->cfg.num_experts * sizeof(float),
+                                cudaMemcpyDeviceToDevice, reinterpret_cast<cudaStream_t>(stream)));
+  return B200MOE_OK;
+}
+
+// ------------------------------------------------------------------------------------------
+// expert execution
+// ------------------------------------------------------------------------------------------
+static int upload_layer_table(b200moe_ctx* ctx, int layer, cudaStream_t st) {
+  if (!ctx->dirty[layer]) return B200MOE_OK;
+  const int E = ctx->cfg.num_experts;
+  // pageable source: the runtime stages the bytes before returning, and the copy is ordered
+  // behind earlier work of `st` that may still read the old table
+  CUDA_TRY(ctx, cudaMemcpyAsync(ctx->d_experts + (size_t)layer * E, ctx->h_experts.data() + (size_t)layer * E,
+                                E * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, st));
+  ctx->dirty[layer] = 0;
+  return B200MOE_OK;
+}
+
+struct FfnLaunch {
+  const ExpertPtrs* experts;
+  const int* offsets;
+  const int* sorted_pair;
+  const int* act_list;
+  const int* n_act;
+  const void* x;
+  void* h;
+  void* y;
+  int K;        // pairs per token in sorted_pair
+  int max_n;    // upper bound on tokens per expert
+};
+
+template <typename T, int NT> static int launch_gemv_pair(b200moe_ctx* ctx, const FfnParams& p, const SlotTable& st, cudaStream_t s) {
+  const int grid = ctx->sm_count * 2;
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
+    ffn_gemv_kernel<T, NT, true><<<grid, kGemvThreads, 0, s>>>(p, st);
+  }
+  int rc = post_launch(ctx, "ffn_gemv_kernel<gate/up>");
+  if (rc) return rc;
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_FFN_DOWN, s);
+    ffn_gemv_kernel<T, NT, false><<<grid, kGemvThreads, 0, s>>>(p, st);
+  }
+  return post_launch(ctx, "ffn_gemv_kernel<down>");
+}
+
+static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st, int ffn_kind, cudaStream_t s) {
+  const b200moe_config& c = ctx->cfg;
+  FfnParams p{};
+  p.x = f.x; p.h = f.h; p.y = f.y;
+  p.experts = f.experts; p.offsets = f.offsets; p.sorted_pair = f.sorted_pair; p.act_list = f.act_list; p.n_act = f.n_act;
+  p.H = c.hidden_size; p.I = c.intermediate_size; p.K = f.K;
+  if (c.weight_mode == B200MOE_W_INT4_G128) {
+#ifdef B200MOE_WITH_INT4
+    return launch_ffn_int4(ctx->sm_count, p, st, f.max_n, s, [&](const char* what) { return post_launch(ctx, what); });
+#else
+    return fail(ctx, B200MOE_E_UNSUPPORTED, "library built without the int4 kernels");
+#endif
+  }
+#ifdef B200MOE_WITH_UMMA
+  if (c.act_dtype == B200MOE_BF16 && ffn_kind != B200MOE_FFN_GEMV && (ffn_kind == B200MOE_FFN_MMA || f.max_n > 4)) {
+    int rc = launch_ffn_umma(ctx, p, st, f.max_n, s);
+    if (rc != B200MOE_E_UNSUPPORTED) return rc;
+    if (ffn_kind == B200MOE_FFN_MMA) return rc;
+  }
+#else
+  if (ffn_kind == B200MOE_FFN_MMA) return fail(ctx, B200MOE_E_UNSUPPORTED, "library built without the tensor-core kernels");
+#endif
+  return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
+    using T = decltype(tag);
+    if (f.max_n <= 1) return launch_gemv_pair<T, 1>(ctx, p, st, s);
+    if (f.max_n <= 2) return launch_gemv_pair<T, 2>(ctx, p, st, s);
+    return launch_gemv_pair<T, 4>(ctx, p, st, s);
+  });
+}
+
+static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const int64_t* ids, const void* scores,
+                       int scores_dtype, const int32_t* expert_slot, const int32_t* order, const void* residual,
+                       void* out, int ffn_kind, cudaStream_t st) {
+  const b200moe_config& c = ctx->cfg;
+  const int E = c.num_experts;
+  SlotTable tab;
+  for (int e = 0; e < kMaxExperts; ++e) { tab.slot[e] = -1; tab.rank[e] = (uint8_t)(e & 255); }
+  for (int e = 0; e < E; ++e) {
+    int s = expert_slot ? expert_slot[e] : e;
+    if (s >= E) return fail(ctx, B200MOE_E_ARG, "expert_slot[%d]=%d out of range", e, s);
+    if (s >= 0 && !ctx->registered[(size_t)layer * E + s]) s = -1;
+    tab.slot[e] = (int16_t)(s < 0 ? -1 : s);
+    if (order) {
+      if (order[e] < 0 || order[e] > 255) return fail(ctx, B200MOE_E_ARG, "order[%d]=%d out of range [0,255]", e, order[e]);
+      tab.rank[e] = (uint8_t)order[e];
+    }
+  }
+  int rc = upload_layer_table(ctx, layer, st);
+  if (rc) return rc;
+
+  PermuteParams pp{};
+  pp.ids64 = ids; pp.T = T; pp.K = c.top_k; pp.E = E;
+  pp.offsets = ctx->offsets; pp.sorted_pair = ctx->sorted_pair; pp.inv = ctx->inv;
+  pp.act_list = ctx->act_list; pp.n_act = ctx->n_act; pp.status = ctx->status;
+  const size_t smem = (size_t)(kPermuteWarps * E + 2 * E + 1) * sizeof(int);
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_PERMUTE, st);
+    permute_kernel<<<1, kPermuteThreads, smem, st>>>(pp, tab);
+  }
+  if ((rc = post_launch(ctx, "permute_kernel"))) return rc;
+
+  FfnLaunch f{};
+  f.experts = ctx->d_experts + (size_t)layer * E;
+  f.offsets = ctx->offsets; f.sorted_pair = ctx->sorted_pair; f.act_list = ctx->act_list; f.n_act = ctx->n_act;
+  f.x = x; f.h = ctx->h; f.y = ctx->y; f.K = c.top_k; f.max_n = T;
+  if ((rc = launch_ffn(ctx, f, tab, ffn_kind, st))) return rc;
+
+  CombineParams cp{};
+  cp.y = ctx->y; cp.inv = ctx->inv; cp.ids64 = ids; cp.scores = scores;
+  cp.scores_f32 = (scores_dtype == B200MOE_F32 && c.act_dtype != B200MOE_F32) ? 1 : 0;
+  cp.residual = residual; cp.out = out; cp.T = T; cp.H = c.hidden_size; cp.K = c.top_k; cp.E = E;
+  return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
+    using Tt = decltype(tag);
+    ProfScope prof(ctx, B200MOE_KERNEL_COMBINE, st);
+    combine_kernel<Tt><<<T, kCombineThreads, 0, st>>>(cp, tab);
+    return post_launch(ctx, "combine_kernel");
+  });
+}
+
+extern "C" int b200moe_forward(b200moe_ctx* ctx, int layer, const void* x, int T, const int64_t* ids, const void* scores,
+                               int scores_dtype, const int32_t* expert_slot, const int32_t* order, const void* residual,
+                               void* out, int ffn_kind, void* stream) {
+  int rc = check_layer(ctx, layer, "b200moe_forward");
+  if (rc) return rc;
+  if ((rc = check_tokens(ctx, T, "b200moe_forward"))) return rc;
+  if (T == 0) return B200MOE_OK;
+  if (!x || !ids || !scores || !out) return fail(ctx, B200MOE_E_ARG, "b200moe_forward: null pointer");
+  if (misaligned(x) || misaligned(out) || (residual && misaligned(residual)))
+    return fail(ctx, B200MOE_E_ARG, "b200moe_forward: x, out and residual must be 16-byte aligned");
+  if (scores_dtype != ctx->cfg.act_dtype && scores_dtype != B200MOE_F32)
+    return fail(ctx, B200MOE_E_ARG, "b200moe_forward: scores must be in the activation dtype or fp32");
+  if (ffn_kind < B200MOE_FFN_AUTO || ffn_kind > B200MOE_FFN_MMA) return fail(ctx, B200MOE_E_ARG, "b200moe_forward: unknown ffn_kind %d", ffn_kind);
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  return run_experts(ctx, layer, x, T, ids, scores, scores_dtype, expert_slot, order, residual, out, ffn_kind,
+                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200moe_forward_fused(b200moe_ctx* ctx, int layer, const void* x, int T, const void* residual, void* out,
+                                     int64_t* ids_out, void* scores_out, int ffn_kind, void* stream) {
+  int rc = check_layer(ctx, layer, "b200moe_forward_fused");
+  if (rc) return rc;
+  if ((rc = check_tokens(ctx, T, "b200moe_forward_fused"))) return rc;
+  if (T == 0) return B200MOE_OK;
+  if (!x || !out) return fail(ctx, B200MOE_E_ARG, "b200moe_forward_fused: null pointer");
+  if (misaligned(x) || misaligned(out) || (residual && misaligned(residual)))
+    return fail(ctx, B200MOE_E_ARG, "b200moe_forward_fused: x, out and residual must be 16-byte aligned");
+  if (!ctx->gate_w[layer]) return fail(ctx, B200MOE_E_STATE, "b200moe_forward_fused: no gate weight registered for layer %d", layer);
+  if (ffn_kind < B200MOE_FFN_AUTO || ffn_kind > B200MOE_FFN_MMA) return fail(ctx, B200MOE_E_ARG, "b200moe_forward_fused: unknown ffn_kind %d", ffn_kind);
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int64_t* ids = ids_out ? ids_out : ctx->ids64;
+  void* scores = scores_out ? scores_out : ctx->scores;
+  if ((rc = launch_router(ctx, layer, x, nullptr, T, ids, scores, nullptr, st))) return rc;
+  return run_experts(ctx, layer, x, T, ids, scores, ctx->cfg.act_dtype, nullptr, nullptr, residual, out, ffn_kind, st);
+}
+
+extern "C" int b200moe_expert_ffn(b200moe_ctx* ctx, const void* x, int n, const void* gate_proj, const void* up_proj,
+                                  const void* down_proj, void* out, void* stream) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_expert_ffn: null context");
+  const b200moe_config& c = ctx->cfg;
+  if (c.weight_mode != B200MOE_W_DENSE) return fail(ctx, B200MOE_E_UNSUPPORTED, "b200moe_expert_ffn: dense weights only");
+  if (n < 0) return fail(ctx, B200MOE_E_ARG, "b200moe_expert_ffn: negative row count");
+  if ((size_t)n > (size_t)c.max_tokens * c.top_k) return fail(ctx, B200MOE_E_STATE, "b200moe_expert_ffn: n=%d exceeds max_tokens*top_k=%d", n, c.max_tokens * c.top_k);
+  if (n == 0) return B200MOE_OK;
+  if (!x || !gate_proj || !up_proj || !down_proj || !out) return fail(ctx, B200MOE_E_ARG, "b200moe_expert_ffn: null pointer");
+  if (misaligned(x) || misaligned(gate_proj) || misaligned(up_proj) || misaligned(down_proj) || misaligned(out))
+    return fail(ctx, B200MOE_E_ARG, "b200moe_expert_ffn: pointers must be 16-byte aligned");
+  CUDA_TRY(ctx, cudaSetDevice(c.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  ExpertPtrs ep{};
+  ep.w[0] = gate_proj; ep.w[1] = up_proj; ep.w[2] = down_proj;
+  ExpertPtrs* slot = ctx->d_experts + (size_t)c.num_layers * c.num_experts;
+  const int offs[2] = {0, n};
+  CUDA_TRY(ctx, cudaMemcpyAsync(slot, &ep, sizeof ep, cudaMemcpyHostToDevice, st));
+  CUDA_TRY(ctx, cudaMemcpyAsync(ctx->one_offsets, offs, sizeof offs, cudaMemcpyHostToDevice, st));
+  SlotTable tab;
+  for (int e = 0; e < kMaxExperts; ++e) { tab.slot[e] = -1; tab.rank[e] = 0; }
+  tab.slot[0] = 0;
+  FfnLaunch f{};
+  f.experts = slot; f.offsets = ctx->one_offsets; f.sorted_pair = ctx->one_sorted; f.act_list = ctx->one_act; f.n_act = ctx->one_nact;
+  f.x = x; f.h = ctx->h; f.y = out; f.K = 1; f.max_n = n;
+  return launch_ffn(ctx, f, tab, B200MOE_FFN_AUTO, st);
+}
+
+// ------------------------------------------------------------------------------------------
+// int4 pack / unpack, status
+// ------------------------------------------------------------------------------------------
+extern "C" int b200moe_pack_int4(const void* w, int out_features, int in_features, int dtype, void* q, void* scales, void* stream) {
+  if (!w || !q || !scales) return fail(nullptr, B200MOE_E_ARG, "b200moe_pack_int4: null pointer");
+  if (out_features <= 0 || in_features <= 0 || in_features % 128) return fail(nullptr, B200MOE_E_ARG, "b200moe_pack_int4: in_features must be a positive multiple of 128");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long warps = (long long)out_features * (in_features / 128);
+  const long long blocks = (warps * 32 + 255) / 256;
+  if (blocks > 0x7fffffffLL) return fail(nullptr, B200MOE_E_ARG, "b200moe_pack_int4: matrix too large");
+  return dispatch_dtype(nullptr, dtype, [&](auto tag) {
+    using T = decltype(tag);
+    pack_int4_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(reinterpret_cast<const T*>(w), out_features, in_features,
+                                                           reinterpret_cast<uint8_t*>(q), reinterpret_cast<__nv_bfloat16*>(scales));
+    return post_launch(nullptr, "pack_int4_kernel");
+  });
+}
+
+extern "C" int b200moe_unpack_int4(const void* q, const void* scales, int out_features, int in_features, int dtype,
+                                   void* q_out, void* w_out, void* stream) {
+  if (!q || (!q_out && !w_out)) return fail(nullptr, B200MOE_E_ARG, "b200moe_unpack_int4: null pointer");
+  if (w_out && !scales) return fail(nullptr, B200MOE_E_ARG, "b200moe_unpack_int4: scales needed to dequantise");
+  if (out_features <= 0 || in_features <= 0 || in_features % 128) return fail(nullptr, B200MOE_E_ARG, "b200moe_unpack_int4: in_features must be a positive multiple of 128");
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const long long nbytes = (long long)out_features * (in_features / 2);
+  const long long blocks = (nbytes + 255) / 256;
+  if (blocks > 0x7fffffffLL) return fail(nullptr, B200MOE_E_ARG, "b200moe_unpack_int4: matrix too large");
+  return dispatch_dtype(nullptr, dtype, [&](auto tag) {
+    using T = decltype(tag);
+    unpack_int4_kernel<T><<<(unsigned)blocks, 256, 0, st>>>(reinterpret_cast<const uint8_t*>(q), reinterpret_cast<const __nv_bfloat16*>(scales),
+                                                             out_features, in_features, reinterpret_cast<int8_t*>(q_out), reinterpret_cast<T*>(w_out));
+    return post_launch(nullptr, "unpack_int4_kernel");
+  });
+}
+
+extern "C" int b200moe_profile(b200moe_ctx* ctx, int enable) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_profile: null context");
+  ctx->profiling = enable != 0;
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_profile_read(b200moe_ctx* ctx, float* total_ms, int32_t* launches) {
+  if (!ctx || !total_ms || !launches) return fail(ctx, B200MOE_E_ARG, "b200moe_profile_read: null argument");
+  for (int i = 0; i < B200MOE_KERNEL_CLASSES; ++i) { total_ms[i] = 0.0f; launches[i] = 0; }
+  int rc = B200MOE_OK;
+  for (auto& r : ctx->prof) {
+    float ms = 0.0f;
+    cudaError_t e = cudaEventSynchronize(r.b);
+    if (e == cudaSuccess) e = cudaEventElapsedTime(&ms, r.a, r.b);
+    if (e != cudaSuccess) rc = fail(ctx, B200MOE_E_CUDA, "b200moe_profile_read: %s", cudaGetErrorString(e));
+    else if (r.cls >= 0 && r.cls < B200MOE_KERNEL_CLASSES) { total_ms[r.cls] += ms; launches[r.cls]++; }
+    cudaEventDestroy(r.a);
+    cudaEventDestroy(r.b);
+  }
+  ctx->prof.clear();
+  return rc;
+}
+
+extern "C" int b200moe_status(b200moe_ctx* ctx, int* device_status_out, void* stream) {
+  if (!ctx || !device_status_out) return fail(ctx, B200MOE_E_ARG, "b200moe_status: null argument");
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int v = 0;
+  CUDA_TRY(ctx, cudaMemcpyAsync(&v, ctx->status, sizeof v, cudaMemcpyDeviceToHost, st));
+  CUDA_TRY(ctx, cudaMemsetAsync(ctx->status, 0, sizeof v, st));
+  CUDA_TRY(ctx, cudaStreamSynchronize(st));
+  *device_status_out = v;
+  if (v) return fail(ctx, B200MOE_E_DEVICE, "device status word = %d", v);
+  return B200MOE_OK;
+}

@@ -1,0 +1,75 @@
+import os
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+ROOT = Path(__file__).resolve().parent.parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+GOLDEN = ROOT / "tests" / "golden"
+_DT = {"float32": torch.float32, "float16": torch.float16, "bfloat16": torch.bfloat16}
+
+
+def pytest_configure(config):
+    config.addinivalue_line("markers", "gpu: needs a CUDA device (B200); run with -m gpu")
+
+
+def pytest_collection_modifyitems(config, items):
+    if torch.cuda.is_available():
+        return
+    skip = pytest.mark.skip(reason="no CUDA device")
+    for item in items:
+        if "gpu" in item.keywords:
+            item.add_marker(skip)
+
+
+def from_np(a: np.ndarray, dtype: torch.dtype) -> torch.Tensor:
+    t = torch.from_numpy(np.ascontiguousarray(a))
+    return t.view(torch.bfloat16) if dtype == torch.bfloat16 else t
+
+
+class Golden:
+    """One fixture written by oracle/pin_against_reference.py."""
+
+    def __init__(self, name: str):
+        self.name = name
+        self.z = np.load(GOLDEN / f"{name}.npz")
+        z = self.z
+        self.H, self.E, self.K, self.I, self.T = (int(z[k]) for k in ("H", "E", "K", "I", "T"))
+        self.layer_idx = int(z["layer_idx"])
+        self.dtype = _DT[str(z["dtype"])]
+        if "gate_w" in z.files:
+            self.gate_w = from_np(z["gate_w"], self.dtype)
+            self.x = from_np(z["x"], self.dtype)
+            self.experts = {e: {k: from_np(z[f"expert{e}_{k}"], self.dtype) for k in ("gate_proj", "up_proj", "down_proj")}
+                            for e in range(self.E)}
+        else:  # large case: inputs are regenerated from the seed and checked against the stored digest
+            from on_device_sd_b200.synth import make_layer
+            layer = make_layer(self.H, self.E, self.K, self.I, self.dtype, self.T, seed=int(z["seed"]))
+            self.gate_w, self.x, self.experts = layer.gate_w, layer.x, layer.experts
+
+    def t(self, key: str) -> torch.Tensor:
+        a = self.z[key]
+        if key.endswith("ids") or key.endswith("order"):
+            return torch.from_numpy(a.astype(np.int64))
+        return from_np(a, self.dtype)
+
+
+GOLDEN_CASES = ["toy_fp32", "tiny_fp16", "small_bf16", "small_fp32"]
+
+
+@pytest.fixture(scope="session", params=GOLDEN_CASES)
+def golden(request):
+    return Golden(request.param)
+
+
+def ulp_tolerance(dtype: torch.dtype) -> float:
+    return {torch.float32: 1e-6, torch.float16: 2.0 ** -11, torch.bfloat16: 2.0 ** -8}[dtype]
+
+
+# BASELINE tolerances for low-precision outputs: max-abs 2e-2, mean-rel 5e-3 (mean|a-b| / mean|b|)
+OUT_TOL = {torch.float32: (1e-5, 1e-5), torch.float16: (2e-2, 5e-3), torch.bfloat16: (2e-2, 5e-3)}

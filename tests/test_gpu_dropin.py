@@ -1,0 +1,126 @@
+"""GPU: the drop-in layer (ModelRunner boundary and nn.Module signatures), written after the
+reference's own tests for this path (demo/tests/unit/test_routing.py, test_forward_moe.py,
+test_engine_optimizations.py:608-749)."""
+import pytest
+import torch
+
+from conftest import OUT_TOL
+from oracle import moe_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture()
+def small():
+    from on_device_sd_b200 import B200MoERunner, MoEShape
+    from on_device_sd_b200.synth import make_named
+    cfg = MoEShape(32, 4, 2, 16, "float16", num_hidden_layers=2)      # the reference's small_config (conftest.py:108-128)
+    runner = B200MoERunner(cfg, max_tokens=16)
+    layers = [make_named("tiny_fp16", 4, seed=s, device="cuda") for s in (0, 1)]
+    for i, L in enumerate(layers):
+        runner.load_gate(i, L.gate_w)
+    return runner, cfg, layers
+
+
+def test_route_experts_output_format(small):
+    from on_device_sd_b200 import ExpertID, RoutingResult
+    runner, cfg, layers = small
+    hidden = torch.randn(1, 4, cfg.hidden_size, device="cuda", dtype=cfg.get_dtype())
+    r = runner.route_experts(layer_idx=0, hidden_states=hidden)
+    assert isinstance(r, RoutingResult) and r.layer_idx == 0
+    assert r.topk_indices.shape == (4, 2) and r.topk_indices.dtype == torch.int64
+    assert r.topk_scores.shape == r.topk_indices.shape and r.topk_scores.dtype == torch.float16
+    s = r.topk_scores.float().sum(-1)
+    assert torch.allclose(s, torch.ones_like(s), atol=2e-3)
+    assert r.activated_expert_ids == {ExpertID(0, i) for i in r.topk_indices.flatten().unique().tolist()}
+    r2 = runner.route_experts(1, hidden.view(4, -1))      # 2-D input is accepted too (qwen3_runner.py:98-99)
+    assert r2.layer_idx == 1 and all(e.layer_idx == 1 for e in r2.activated_expert_ids)
+
+
+def test_forward_moe_matches_oracle_with_residual(small):
+    from on_device_sd_b200 import AttentionOutput, ExpertPlacement
+    runner, cfg, layers = small
+    L = layers[0]
+    hidden = L.x.view(1, 4, -1)
+    r = runner.route_experts(0, hidden)
+    placement = ExpertPlacement(gpu_expert_params=L.experts, cpu_expert_params={}, routing_result=r)
+    out = runner.forward_moe(0, AttentionOutput(hidden, hidden, hidden), placement)
+    assert out.shape == hidden.shape
+    cpu = {e: {k: v.cpu() for k, v in p.items()} for e, p in L.experts.items()}
+    want = O.moe_engine(L.x.cpu(), r.topk_indices.cpu(), r.topk_scores.cpu(), cpu,
+                        order=[e.expert_idx for e in r.activated_expert_ids], residual=L.x.cpu())
+    assert O.max_abs(out.cpu().view(4, -1), want) <= 1e-3       # the reference's path-vs-path tolerance (test_forward_moe.py:66)
+    assert torch.equal(runner._execute_moe_with_placement(hidden, ExpertPlacement({}, {}, {}, None)), torch.zeros_like(hidden))
+
+
+def test_cpu_vs_gpu_placement_close(small):
+    """test_forward_moe.py:44-66 with duplicate-free ids: CPU-resident parameters give the same result."""
+    from on_device_sd_b200 import AttentionOutput, ExpertID, ExpertPlacement, RoutingResult
+    runner, cfg, layers = small
+    L = layers[0]
+    hidden = L.x.view(1, 4, -1)
+    ids = torch.tensor([[0, 1], [1, 2], [3, 0], [2, 3]], device="cuda")
+    scores = torch.full((4, 2), 0.5, device="cuda", dtype=torch.float32)
+    r = RoutingResult(0, ids, scores, {ExpertID(0, i) for i in range(4)})
+    attn = AttentionOutput(hidden, hidden, hidden)
+    gpu_out = runner.forward_moe(0, attn, ExpertPlacement(gpu_expert_params=L.experts, cpu_expert_params={}, routing_result=r))
+    cpu = {e: {k: v.cpu() for k, v in p.items()} for e, p in L.experts.items()}
+    cpu_out = runner.forward_moe(0, attn, ExpertPlacement(gpu_expert_params={}, cpu_expert_params=cpu, routing_result=r))
+    assert torch.allclose(gpu_out, cpu_out, atol=1e-3)
+    assert gpu_out.abs().sum() > 0
+
+
+def test_substitution_uses_substitute_params(small):
+    from on_device_sd_b200 import ExpertID, ExpertPlacement, RoutingResult
+    runner, cfg, layers = small
+    L = layers[0]
+    ids = torch.tensor([[1, 3]] * 4, device="cuda")
+    scores = torch.tensor([[0.25, 0.75]] * 4, device="cuda", dtype=torch.float16)
+    r = RoutingResult(0, ids, scores, {ExpertID(0, 1), ExpertID(0, 3)})
+    pl = ExpertPlacement(gpu_expert_params={0: L.experts[0]}, cpu_expert_params={}, substitution_map={1: 0}, routing_result=r)
+    out = runner._execute_moe_with_placement(L.x, pl)
+    want = (O.expert_ffn(L.x.cpu(), **{k: v.cpu() for k, v in L.experts[0].items()}) * 0.25).half()   # expert 3 skipped
+    assert O.max_abs(out.cpu(), want) <= 1e-3 and out.abs().sum() > 0
+
+
+def test_module_dropins_match_oracle():
+    from on_device_sd_b200 import Qwen3MoEGate, Qwen3MoELayer, Qwen3MoELayerWithWeights
+    from on_device_sd_b200.synth import make_layer
+    H, E, K, I, T = 128, 8, 2, 64, 12
+    L = make_layer(H, E, K, I, torch.bfloat16, T, seed=2)
+    x3 = L.x.cuda().view(2, 6, H)
+    gate = Qwen3MoEGate(H, E).to(torch.bfloat16).cuda()
+    gate.load_weights(L.gate_w.cuda())
+    idx, w = gate(x3, K)
+    o_ids, o_sc, _ = O.route(L.x, L.gate_w, K)
+    assert idx.shape == (2, 6, K) and torch.equal(idx.view(T, K).cpu(), o_ids)
+    assert O.max_abs(w.view(T, K).cpu().float(), o_sc.float()) <= 2 ** -8
+    dev = {e: {k: v.cuda() for k, v in p.items()} for e, p in L.experts.items()}
+    layer = Qwen3MoELayer(H, E, K, I, 0).to(torch.bfloat16).cuda()
+    layer.gate.load_weights(L.gate_w.cuda())
+    out = layer(x3, dev)
+    want = O.moe_layer(L.x, L.gate_w, L.experts, K)
+    tol_a, tol_r = OUT_TOL[torch.bfloat16]
+    assert out.shape == x3.shape and O.max_abs(out.view(T, H).cpu(), want) <= tol_a and O.mean_rel(out.view(T, H).cpu(), want) <= 1e-3
+    out2 = Qwen3MoELayerWithWeights(H, E, K, I, 0)(x3, L.gate_w.cuda(), dev)
+    assert torch.equal(out2, out)
+    # experts missing from the dict are skipped silently (moe_layer.py:136-137)
+    part = {e: dev[e] for e in (0, 3, 5)}
+    want = O.moe_layer(L.x, L.gate_w, {e: L.experts[e] for e in (0, 3, 5)}, K)
+    got = layer(x3, part)
+    assert O.mean_rel(got.view(T, H).cpu(), want) <= 1e-3
+
+
+def test_exact_logits_mode_reproduces_torch_router():
+    """exact_logits=True: ids equal torch's own router on this GPU for every token."""
+    from on_device_sd_b200 import B200MoERunner, MoEShape
+    cfg = MoEShape(2048, 128, 8, 768, "bfloat16")
+    runner = B200MoERunner(cfg, max_tokens=256, exact_logits=True)
+    g = torch.Generator(device="cuda").manual_seed(0)
+    gate_w = (torch.randn(128, 2048, device="cuda", generator=g) * 0.02).bfloat16()
+    x = torch.randn(256, 2048, device="cuda", generator=g).bfloat16()
+    runner.load_gate(0, gate_w)
+    r = runner.route_experts(0, x)
+    vals, ids = torch.topk(torch.nn.functional.linear(x, gate_w), 8, dim=-1)
+    assert torch.equal(r.topk_indices, ids)
+    assert O.max_abs(r.topk_scores.float().cpu(), torch.softmax(vals, -1).float().cpu()) <= 2 ** -8
