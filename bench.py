@@ -129,7 +129,7 @@ def cpu_reference_sweep(layer_cpu, batches, K, repeats_budget_s: float, steps: i
             if steps is not None:
                 if n >= steps:
                     break
-            elif time.time() - t0 >= repeats_budget_s or n >= 3:
+            elif time.time() - t0 >= repeats_budget_s:
                 break
         dt = time.time() - t0
     return sum(batches) * n / dt, dt, n
@@ -262,6 +262,15 @@ def run_ours(args, workload):
     tokens_per_step = sum(batches)
     value = world * tokens_per_step * args.steps / (ms * 1e-3)
 
+    if args.quick:
+        if rank == 0:
+            sampler.stop()
+            print(json.dumps({"metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "ms_per_step": ms / args.steps,
+                              "gpu_launches": launches, "config": {"workload": workload, "token_batches": list(batches)}, "quick": True}), flush=True)
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
     # per-kernel CUDA-event durations: the same steps again with every launch bracketed by events
     ctx.profile(True)
     for _ in range(args.steps):
@@ -368,7 +377,12 @@ def main():
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
     ap.add_argument("--workload", default="mixtral_bf16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--batches", default=None, help="comma-separated token batches replacing the workload's sweep (profiling runs)")
+    ap.add_argument("--quick", action="store_true", help="timed region only: no e2e, per-T or CPU-baseline legs (for ncu captures)")
     args = ap.parse_args()
+    if args.batches:
+        cfg, wm, _ = WORKLOADS[args.workload]
+        WORKLOADS[args.workload] = (cfg, wm, tuple(int(b) for b in args.batches.split(",")))
     if args.impl == "reference":
         run_reference(args, args.workload)
     else:

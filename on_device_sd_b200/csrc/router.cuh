@@ -220,23 +220,39 @@ template <typename T> __global__ void __launch_bounds__(kRouterThreads) router_k
     float xn[TT];
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) { acc[tt] = 0; xn[tt] = 0.0f; }
-    for (int c = lane; c < nch; c += 32) {
-      Chunk<T> wc;
-      wc.template load<false>(wrow + c * 8);
-      float wf[8];
-      wc.unpack(wf);
+    // two chunk positions per trip, all ten loads issued before the first use: the loop is
+    // latency-bound (a warp owns one expert row), so loads in flight are what matter
+    constexpr int U = 2;
+    for (int c0 = lane; c0 < nch; c0 += 32 * U) {
+      Chunk<T> wc[U], xc[U][TT];
 #pragma unroll
-      for (int tt = 0; tt < TT; ++tt) {
-        const int t = min(t0 + tt, p.T - 1);
-        Chunk<T> xc;
-        xc.template load<false>(x + (size_t)t * p.H + c * 8);
-        float xf[8];
-        xc.unpack(xf);
+      for (int u = 0; u < U; ++u) {
+        const int c = c0 + 32 * u;
+        if (c < nch) {
+          wc[u].template load<false>(wrow + c * 8);
 #pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          if (kExact) acc[tt] = fma((double)xf[i], (double)wf[i], acc[tt]);
-          else acc[tt] = fmaf(xf[i], wf[i], acc[tt]);
-          if (do_norm) xn[tt] = fmaf(xf[i], xf[i], xn[tt]);
+          for (int tt = 0; tt < TT; ++tt)
+            xc[u][tt].template load<false>(x + (size_t)min(t0 + tt, p.T - 1) * p.H + c * 8);
+        } else {
+          wc[u].zero();
+#pragma unroll
+          for (int tt = 0; tt < TT; ++tt) xc[u][tt].zero();
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < U; ++u) {
+        float wf[8];
+        wc[u].unpack(wf);
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+          float xf[8];
+          xc[u][tt].unpack(xf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (kExact) acc[tt] = fma((double)xf[i], (double)wf[i], acc[tt]);
+            else acc[tt] = fmaf(xf[i], wf[i], acc[tt]);
+            if (do_norm) xn[tt] = fmaf(xf[i], xf[i], xn[tt]);
+          }
         }
       }
     }

@@ -24,11 +24,19 @@ def _register(ctx, experts, layer=0):
 
 
 def _close(got, want, dtype, tight=False):
-    ma, mr = O.max_abs(got.cpu(), want.cpu()), O.mean_rel(got.cpu(), want.cpu())
+    """max-abs <= 2e-2 and mean-rel <= 5e-3 for 16-bit outputs (1e-5 for fp32).  The absolute bound
+    is widened by two units in the last place of the expected value (2 * 2^-7 |y| for bf16,
+    2 * 2^-10 |y| for fp16): with N(0, 0.02) weights the Mixtral-shaped layer produces |y| up to ~16,
+    where ONE bf16 ulp is 0.0625 > 2e-2; a last-bit difference in one expert's output (fp32 summation
+    order) can move the two-term bf16 accumulation by two ulps.  mean-rel is the sharp criterion."""
+    got, want = got.cpu().double(), want.cpu().double()
+    ma, mr = O.max_abs(got, want), O.mean_rel(got, want)
     tol_a, tol_r = OUT_TOL[dtype]
     if tight and dtype != torch.float32:
         tol_r = 1e-3     # same rounding points and same accumulation order: far inside the budget
-    assert ma <= tol_a and mr <= tol_r, (ma, mr)
+    ulp = {torch.float32: 0.0, torch.float16: 2.0 ** -9, torch.bfloat16: 2.0 ** -6}[dtype]
+    excess = float(((got - want).abs() - (tol_a + ulp * want.abs())).max()) if got.numel() else -1.0
+    assert excess <= 0 and mr <= tol_r, (ma, mr, excess)
     return ma, mr
 
 
@@ -164,9 +172,6 @@ def test_qwen3_shape_reduced_experts(T):
     out_b = ctx.forward(0, L.x.cuda(), ids, scores, order=_rank(order, 32))
     _close(out_b, want_b, torch.bfloat16, tight=True)
     assert ctx.status() == 0
-
-
-_QWEN_CACHE = {}
 
 
 def _device_oracle(L, ids, scores, order):
