@@ -84,7 +84,7 @@ int b200moe_destroy(b200moe_ctx* ctx);
 /* Registers the router weight Wg [E, H] of `layer` (nn.Linear.weight of Qwen3MoEGate,
  * demo/src/layers/moe_layer.py:20-23, loaded by load_weights :62-65) and an optional logit
  * bias [E] in the activation dtype (NULL in the reference; used by the popularity-skew
- * stress configuration).  Enqueues a small kernel that caches the squared row norms of Wg. */
+ * stress configuration).  Host-side bookkeeping only; `stream` is unused. */
 int b200moe_set_gate(b200moe_ctx* ctx, int layer, const void* gate_weight, const void* bias_or_null,
                      void* stream);
 

@@ -2,10 +2,12 @@
 // workspace, expert pointer tables and kernel launches.  No torch types, no CPU compute path.
 #include "../../include/b200moe.h"
 
+#include <cuda.h>
 #include <cuda_runtime.h>
 
 #include <cstdarg>
 #include <cstdio>
+#include <cstdlib>
 #include <cstring>
 #include <new>
 #include <string>
@@ -28,6 +30,7 @@ using namespace b200moe;
 struct b200moe_ctx {
   b200moe_config cfg{};
   int sm_count = 0;
+  int gemv_variant = 0;
   std::string err;
   int64_t launches = 0;
   // registered weights (host mirror) and the device table
@@ -36,10 +39,15 @@ struct b200moe_ctx {
   std::vector<uint8_t> registered;
   std::vector<uint8_t> dirty;
   ExpertPtrs* d_experts = nullptr;  // [L*E (+1 scratch entry for expert_ffn)]
-  float* wnorm2 = nullptr;          // [L*E]
+#ifdef B200MOE_WITH_UMMA
+  // TMA descriptors of the registered experts (dense bf16 only): [L*E + 1][3], host mirror + device copy
+  std::vector<CUtensorMap> h_tmaps;
+  std::vector<uint8_t> tmap_ok;
+  CUtensorMap* d_tmaps = nullptr;
+  void* encode_fn = nullptr;   // cuTensorMapEncodeTiled, resolved through the runtime
+#endif
   // workspace
-  float* logit_sum = nullptr;
-  float* xnorm2 = nullptr;
+  float* logits = nullptr;          // [Tm,E] rounded logits of the latest router launch, as fp32
   unsigned* tile_counter = nullptr;
   int64_t* ids64 = nullptr;
   void* scores = nullptr;
@@ -147,6 +155,7 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
   if (!ctx) return fail(nullptr, B200MOE_E_CUDA, "out of host memory");
   ctx->cfg = *cfg;
   ctx->sm_count = prop.multiProcessorCount;
+  if (const char* v = getenv("B200MOE_GEMV_VARIANT")) ctx->gemv_variant = atoi(v);
   const size_t L = cfg->num_layers, Tm = cfg->max_tokens, eb = elem_bytes(cfg->act_dtype);
   ctx->gate_w.assign(L, nullptr);
   ctx->gate_bias.assign(L, nullptr);
@@ -158,8 +167,7 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
   char* yb = nullptr;
   char* sb = nullptr;
   const size_t pairs = Tm * K;
-  if ((rc = dev_alloc(ctx, &ctx->d_experts, L * E + 1)) || (rc = dev_alloc(ctx, &ctx->wnorm2, L * E)) ||
-      (rc = dev_alloc(ctx, &ctx->logit_sum, Tm * E)) || (rc = dev_alloc(ctx, &ctx->xnorm2, Tm)) ||
+  if ((rc = dev_alloc(ctx, &ctx->d_experts, L * E + 1)) || (rc = dev_alloc(ctx, &ctx->logits, Tm * E)) ||
       (rc = dev_alloc(ctx, &ctx->tile_counter, Tm)) || (rc = dev_alloc(ctx, &ctx->ids64, pairs)) ||
       (rc = dev_alloc(ctx, &sb, pairs * 4)) || (rc = dev_alloc(ctx, &ctx->offsets, (size_t)E + 1)) ||
       (rc = dev_alloc(ctx, &ctx->sorted_pair, pairs)) || (rc = dev_alloc(ctx, &ctx->inv, pairs)) ||
@@ -175,6 +183,21 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
   ctx->h = hb;
   ctx->y = yb;
   ctx->scores = sb;
+#ifdef B200MOE_WITH_UMMA
+  if (cfg->act_dtype == B200MOE_BF16 && cfg->weight_mode == B200MOE_W_DENSE) {
+    ctx->h_tmaps.assign((L * E + 1) * 3, CUtensorMap{});
+    ctx->tmap_ok.assign(L * E + 1, 0);
+    if ((rc = dev_alloc(ctx, &ctx->d_tmaps, (L * E + 1) * 3))) {
+      std::string msg = ctx->err;
+      b200moe_destroy(ctx);
+      return fail(nullptr, rc, "%s", msg.c_str());
+    }
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->encode_fn, cudaEnableDefault, &qres) != cudaSuccess ||
+        qres != cudaDriverEntryPointSuccess)
+      ctx->encode_fn = nullptr;   // the tensor-core path then reports itself unsupported
+  }
+#endif
   cudaMemset(ctx->tile_counter, 0, Tm * sizeof(unsigned));
   cudaMemset(ctx->status, 0, sizeof(int));
   cudaMemset(ctx->d_experts, 0, (L * E + 1) * sizeof(ExpertPtrs));
@@ -232,6 +255,31 @@ static int post_launch(b200moe_ctx* ctx, const char* what) {
   return B200MOE_OK;
 }
 
+#ifdef B200MOE_WITH_UMMA
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// bf16 matrix [rows, cols] row-major -> 2-D tensor map with a {64 cols, box_rows} box, 128-byte swizzle
+static bool encode_map(b200moe_ctx* ctx, CUtensorMap* out, const void* base, int rows, int cols, int box_rows) {
+  if (!ctx->encode_fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
+  const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
+  const cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_fn)(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+                                                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
+static bool encode_expert_maps(b200moe_ctx* ctx, CUtensorMap* three, const void* gate, const void* up, const void* down) {
+  const int H = ctx->cfg.hidden_size, I = ctx->cfg.intermediate_size;
+  return encode_map(ctx, &three[0], gate, I, H, 64) && encode_map(ctx, &three[1], up, I, H, 64) &&
+         encode_map(ctx, &three[2], down, H, I, 128);
+}
+#endif
+
 extern "C" int b200moe_set_gate(b200moe_ctx* ctx, int layer, const void* gate_weight, const void* bias_or_null, void* stream) {
   int rc = check_layer(ctx, layer, "b200moe_set_gate");
   if (rc) return rc;
@@ -239,14 +287,8 @@ extern "C" int b200moe_set_gate(b200moe_ctx* ctx, int layer, const void* gate_we
   CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
   ctx->gate_w[layer] = gate_weight;
   ctx->gate_bias[layer] = bias_or_null;
-  const int E = ctx->cfg.num_experts, H = ctx->cfg.hidden_size;
-  float* wn = ctx->wnorm2 + (size_t)layer * E;
-  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  return dispatch_dtype(ctx, ctx->cfg.act_dtype, [&](auto tag) {
-    using T = decltype(tag);
-    gate_norm_kernel<T><<<(E * 32 + 255) / 256, 256, 0, st>>>(reinterpret_cast<const T*>(gate_weight), wn, E, H);
-    return post_launch(ctx, "gate_norm_kernel");
-  });
+  (void)stream;  // nothing is enqueued: the pointers are read by later router launches
+  return B200MOE_OK;
 }
 
 extern "C" int b200moe_set_expert(b200moe_ctx* ctx, int layer, int expert, const void* gate_proj, const void* up_proj,
@@ -269,6 +311,12 @@ extern "C" int b200moe_set_expert(b200moe_ctx* ctx, int layer, int expert, const
   ep.s[0] = gate_scales; ep.s[1] = up_scales; ep.s[2] = down_scales;
   ctx->registered[(size_t)layer * E + expert] = 1;
   ctx->dirty[layer] = 1;
+#ifdef B200MOE_WITH_UMMA
+  if (!ctx->h_tmaps.empty()) {
+    const size_t idx = (size_t)layer * E + expert;
+    ctx->tmap_ok[idx] = encode_expert_maps(ctx, &ctx->h_tmaps[idx * 3], gate_proj, up_proj, down_proj) ? 1 : 0;
+  }
+#endif
   return B200MOE_OK;
 }
 
@@ -295,10 +343,8 @@ static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void*
   if (!logits) {
     p.wg = ctx->gate_w[layer];
     p.bias = ctx->gate_bias[layer];
-    p.wnorm2 = ctx->wnorm2 + (size_t)layer * c.num_experts;
   }
-  p.logit_sum = ctx->logit_sum;
-  p.xnorm2 = ctx->xnorm2;
+  p.logits = ctx->logits;
   p.tile_counter = ctx->tile_counter;
   p.ids64 = ids_out;
   p.scores = scores_out;
@@ -311,8 +357,12 @@ static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void*
       router_from_logits_kernel<Tt><<<(T + 7) / 8, kRouterThreads, 0, st>>>(p);
       return post_launch(ctx, "router_from_logits_kernel");
     }
-    dim3 grid((T + kRouterTokensPerTile - 1) / kRouterTokensPerTile, (c.num_experts + 7) / 8);
-    router_kernel<Tt><<<grid, kRouterThreads, 0, st>>>(p);
+    const unsigned ey = (c.num_experts + 7) / 8;
+    if ((long long)T * ey <= 2LL * ctx->sm_count) {   // small batch: one token per tile, deep unroll
+      router_kernel<Tt, 1, 8><<<dim3(T, ey), kRouterThreads, 0, st>>>(p);
+    } else {
+      router_kernel<Tt, 4, 2><<<dim3((T + 3) / 4, ey), kRouterThreads, 0, st>>>(p);
+    }
     return post_launch(ctx, "router_kernel");
   });
 }
@@ -355,7 +405,7 @@ extern "C" int b200moe_last_logits(b200moe_ctx* ctx, int T, float* logits_out, v
   int rc = check_tokens(ctx, T, "b200moe_last_logits");
   if (rc) return rc;
   CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
-  CUDA_TRY(ctx, cudaMemcpyAsync(logits_out, ctx->logit_sum, (size_t)T * ctx->cfg.num_experts * sizeof(float),
+  CUDA_TRY(ctx, cudaMemcpyAsync(logits_out, ctx->logits, (size_t)T * ctx->cfg.num_experts * sizeof(float),
                                 cudaMemcpyDeviceToDevice, reinterpret_cast<cudaStream_t>(stream)));
   return B200MOE_OK;
 }
@@ -370,6 +420,11 @@ static int upload_layer_table(b200moe_ctx* ctx, int layer, cudaStream_t st) {
   // behind earlier work of `st` that may still read the old table
   CUDA_TRY(ctx, cudaMemcpyAsync(ctx->d_experts + (size_t)layer * E, ctx->h_experts.data() + (size_t)layer * E,
                                 E * sizeof(ExpertPtrs), cudaMemcpyHostToDevice, st));
+#ifdef B200MOE_WITH_UMMA
+  if (!ctx->h_tmaps.empty())
+    CUDA_TRY(ctx, cudaMemcpyAsync(ctx->d_tmaps + (size_t)layer * E * 3, ctx->h_tmaps.data() + (size_t)layer * E * 3,
+                                  (size_t)E * 3 * sizeof(CUtensorMap), cudaMemcpyHostToDevice, st));
+#endif
   ctx->dirty[layer] = 0;
   return B200MOE_OK;
 }
@@ -384,23 +439,81 @@ struct FfnLaunch {
   void* h;
   void* y;
   int K;        // pairs per token in sorted_pair
+  const void* tmaps;  // tensor maps matching `experts` (null when the tensor-core path cannot run)
   int max_n;    // upper bound on tokens per expert
 };
 
-template <typename T, int NT> static int launch_gemv_pair(b200moe_ctx* ctx, const FfnParams& p, const SlotTable& st, cudaStream_t s) {
-  const int grid = ctx->sm_count * 2;
+using GemvDefault = GemvShape<8, 2048, 3>;
+
+template <typename T, int NT, typename S> static int launch_gemv_pair_shape(b200moe_ctx* ctx, const FfnParams& p, const SlotTable& st, cudaStream_t s) {
+  const int grid = ctx->sm_count;   // one persistent CTA per SM: the rings take most of its shared memory
+  auto up = ffn_gemv_kernel<T, NT, true, S>;
+  auto down = ffn_gemv_kernel<T, NT, false, S>;
+  static bool configured = false;   // per template instance
+  if (!configured) {
+    CUDA_TRY(ctx, cudaFuncSetAttribute(up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
+    CUDA_TRY(ctx, cudaFuncSetAttribute(down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
+    configured = true;
+  }
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
-    ffn_gemv_kernel<T, NT, true><<<grid, kGemvThreads, 0, s>>>(p, st);
+    up<<<grid, S::THREADS, S::SMEM, s>>>(p, st, ctx->status);
   }
   int rc = post_launch(ctx, "ffn_gemv_kernel<gate/up>");
   if (rc) return rc;
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_DOWN, s);
-    ffn_gemv_kernel<T, NT, false><<<grid, kGemvThreads, 0, s>>>(p, st);
+    down<<<grid, S::THREADS, S::SMEM, s>>>(p, st, ctx->status);
   }
   return post_launch(ctx, "ffn_gemv_kernel<down>");
 }
+
+template <typename T, int NT> static int launch_gemv_pair(b200moe_ctx* ctx, const FfnParams& p, const SlotTable& st, cudaStream_t s) {
+  switch (ctx->gemv_variant) {   // tuning knob (environment variable B200MOE_GEMV_VARIANT at create time)
+    case 1: return launch_gemv_pair_shape<T, NT, GemvShape<16, 1024, 3>>(ctx, p, st, s);
+    case 2: return launch_gemv_pair_shape<T, NT, GemvShape<8, 1024, 6>>(ctx, p, st, s);
+    case 3: return launch_gemv_pair_shape<T, NT, GemvShape<8, 4096, 2>>(ctx, p, st, s);
+    case 4: return launch_gemv_pair_shape<T, NT, GemvShape<16, 2048, 2>>(ctx, p, st, s);
+    default: return launch_gemv_pair_shape<T, NT, GemvDefault>(ctx, p, st, s);
+  }
+}
+
+#ifdef B200MOE_WITH_UMMA
+template <int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, const UmmaParams& up, const SlotTable& st, cudaStream_t s) {
+  using S = UmmaShape<NMAX>;
+  auto k_up = ffn_umma_kernel<NMAX, true>;
+  auto k_down = ffn_umma_kernel<NMAX, false>;
+  static bool configured = false;
+  if (!configured) {
+    CUDA_TRY(ctx, cudaFuncSetAttribute(k_up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
+    CUDA_TRY(ctx, cudaFuncSetAttribute(k_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
+    configured = true;
+  }
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
+    k_up<<<ctx->sm_count, kUmmaThreads, S::SMEM, s>>>(up, st);
+  }
+  int rc = post_launch(ctx, "ffn_umma_kernel<gate/up>");
+  if (rc) return rc;
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_FFN_DOWN, s);
+    k_down<<<ctx->sm_count, kUmmaThreads, S::SMEM, s>>>(up, st);
+  }
+  return post_launch(ctx, "ffn_umma_kernel<down>");
+}
+
+static int launch_ffn_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tmaps, const SlotTable& st, int max_n, cudaStream_t s) {
+  if (!tmaps) return fail(ctx, B200MOE_E_UNSUPPORTED, "tensor-core path unavailable: no TMA descriptors for these experts");
+  UmmaParams up{};
+  up.f = p;
+  up.tmaps = reinterpret_cast<const CUtensorMap*>(tmaps);
+  up.status = ctx->status;
+  if (max_n <= 16) return launch_umma_pair<16>(ctx, up, st, s);
+  if (max_n <= 32) return launch_umma_pair<32>(ctx, up, st, s);
+  if (max_n <= 64) return launch_umma_pair<64>(ctx, up, st, s);
+  return launch_umma_pair<128>(ctx, up, st, s);
+}
+#endif
 
 static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st, int ffn_kind, cudaStream_t s) {
   const b200moe_config& c = ctx->cfg;
@@ -417,7 +530,7 @@ static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st,
   }
 #ifdef B200MOE_WITH_UMMA
   if (c.act_dtype == B200MOE_BF16 && ffn_kind != B200MOE_FFN_GEMV && (ffn_kind == B200MOE_FFN_MMA || f.max_n > 4)) {
-    int rc = launch_ffn_umma(ctx, p, st, f.max_n, s);
+    int rc = launch_ffn_umma(ctx, p, f.tmaps, st, f.max_n, s);
     if (rc != B200MOE_E_UNSUPPORTED) return rc;
     if (ffn_kind == B200MOE_FFN_MMA) return rc;
   }
@@ -467,6 +580,14 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   f.experts = ctx->d_experts + (size_t)layer * E;
   f.offsets = ctx->offsets; f.sorted_pair = ctx->sorted_pair; f.act_list = ctx->act_list; f.n_act = ctx->n_act;
   f.x = x; f.h = ctx->h; f.y = ctx->y; f.K = c.top_k; f.max_n = T;
+#ifdef B200MOE_WITH_UMMA
+  if (!ctx->h_tmaps.empty()) {
+    bool all_ok = true;
+    for (int e = 0; e < E; ++e)
+      if (tab.slot[e] >= 0 && !ctx->tmap_ok[(size_t)layer * E + tab.slot[e]]) all_ok = false;
+    if (all_ok) f.tmaps = ctx->d_tmaps + (size_t)layer * E * 3;
+  }
+#endif
   if ((rc = launch_ffn(ctx, f, tab, ffn_kind, st))) return rc;
 
   CombineParams cp{};
@@ -543,6 +664,15 @@ extern "C" int b200moe_expert_ffn(b200moe_ctx* ctx, const void* x, int n, const 
   FfnLaunch f{};
   f.experts = slot; f.offsets = ctx->one_offsets; f.sorted_pair = ctx->one_sorted; f.act_list = ctx->one_act; f.n_act = ctx->one_nact;
   f.x = x; f.h = ctx->h; f.y = out; f.K = 1; f.max_n = n;
+#ifdef B200MOE_WITH_UMMA
+  if (!ctx->h_tmaps.empty() && n > 4) {
+    const size_t idx = (size_t)c.num_layers * c.num_experts;
+    if (encode_expert_maps(ctx, &ctx->h_tmaps[idx * 3], gate_proj, up_proj, down_proj)) {
+      CUDA_TRY(ctx, cudaMemcpyAsync(ctx->d_tmaps + idx * 3, &ctx->h_tmaps[idx * 3], 3 * sizeof(CUtensorMap), cudaMemcpyHostToDevice, st));
+      f.tmaps = ctx->d_tmaps + idx * 3;
+    }
+  }
+#endif
   return launch_ffn(ctx, f, tab, B200MOE_FFN_AUTO, st);
 }
 

@@ -59,6 +59,10 @@ template <> struct Chunk<float> {
     if (kStream) { a = ldg_stream(p); b = ldg_stream(p + 4); }
     else { a = ldg_cached(p); b = ldg_cached(p + 4); }
   }
+  __device__ __forceinline__ void from_smem(const void* p) {   // 32 bytes
+    a = reinterpret_cast<const uint4*>(p)[0];
+    b = reinterpret_cast<const uint4*>(p)[1];
+  }
   __device__ __forceinline__ void zero() { a = make_uint4(0, 0, 0, 0); b = a; }
   __device__ __forceinline__ void unpack(float (&f)[8]) const {
     f[0] = __uint_as_float(a.x); f[1] = __uint_as_float(a.y); f[2] = __uint_as_float(a.z); f[3] = __uint_as_float(a.w);
@@ -71,6 +75,7 @@ template <> struct Chunk<__nv_bfloat16> {
   template <bool kStream> __device__ __forceinline__ void load(const __nv_bfloat16* p) {
     a = kStream ? ldg_stream(p) : ldg_cached(p);
   }
+  __device__ __forceinline__ void from_smem(const void* p) { a = *reinterpret_cast<const uint4*>(p); }
   __device__ __forceinline__ void zero() { a = make_uint4(0, 0, 0, 0); }
   __device__ __forceinline__ void unpack(float (&f)[8]) const {
     // bf16 -> fp32 is a 16-bit shift
@@ -86,6 +91,7 @@ template <> struct Chunk<__half> {
   template <bool kStream> __device__ __forceinline__ void load(const __half* p) {
     a = kStream ? ldg_stream(p) : ldg_cached(p);
   }
+  __device__ __forceinline__ void from_smem(const void* p) { a = *reinterpret_cast<const uint4*>(p); }
   __device__ __forceinline__ void zero() { a = make_uint4(0, 0, 0, 0); }
   __device__ __forceinline__ void unpack(float (&f)[8]) const {
     const uint32_t w[4] = {a.x, a.y, a.z, a.w};

@@ -11,6 +11,7 @@
 #pragma once
 #include "common.cuh"
 #include "permute.cuh"
+#include "tma.cuh"
 
 namespace b200moe {
 
@@ -31,94 +32,146 @@ struct FfnParams {
   int H, I, K;
 };
 
-constexpr int kGemvThreads = 256;
-constexpr int kGemvWarps = kGemvThreads / 32;
-constexpr int kGemvStreams = 4;   // weight rows a warp streams concurrently
-constexpr int kGemvDepth = 3;     // register stages of the load pipeline
+// Bytes of one row segment, ring depth and warps per CTA of the streaming kernels.  Every warp
+// owns a private ring of STAGES slots x 4 row segments in shared memory, fills it with 1-D bulk
+// copies (TMA) and consumes it itself, so no cross-warp synchronisation exists at all.
+template <int WARPS_, int SEG_, int STAGES_> struct GemvShape {
+  static constexpr int WARPS = WARPS_, SEG = SEG_, STAGES = STAGES_;
+  static constexpr int THREADS = WARPS * 32;
+  static constexpr size_t SMEM = (size_t)WARPS * STAGES * 4 * SEG + (size_t)WARPS * STAGES * 8 + 128;
+};
 
-// DUAL = true : gate/up projections + SwiGLU epilogue, 2 rows x 2 matrices per warp, 16 rows per item
-// DUAL = false: down projection, 4 rows per warp, 32 rows per item
-template <typename T, int NT, bool DUAL>
-__global__ void __launch_bounds__(kGemvThreads, 2) ffn_gemv_kernel(FfnParams p, SlotTable st) {
-  constexpr int RW = DUAL ? 2 : 4;                 // output rows per warp
-  constexpr int ROWS_PER_ITEM = RW * kGemvWarps;
+// DUAL = true : gate/up projections + SwiGLU epilogue; a unit = rows (r, r+1) of gate_proj and up_proj
+// DUAL = false: down projection; a unit = rows (r .. r+3) of down_proj
+// Units are dealt round-robin to the warps of the whole grid.  For every unit the warp streams the
+// four rows once per pass of NT tokens; x (or h) comes through L1 with 16-byte loads.
+template <typename T, int NT, bool DUAL, typename S>
+__global__ void __launch_bounds__(S::THREADS, 1) ffn_gemv_kernel(FfnParams p, SlotTable st, int* status) {
+  constexpr int RW = DUAL ? 2 : 4;
+  constexpr int SEG = S::SEG, STAGES = S::STAGES;
+  constexpr int SEG_ELEMS = SEG / (int)sizeof(T);
+  extern __shared__ __align__(128) unsigned char smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int Kdim = DUAL ? p.H : p.I;               // reduction length
-  const int Rdim = DUAL ? p.I : p.H;               // output rows of the matrix
-  const int nch = Kdim / 8;
-  const int nj = (nch + 31) / 32;
-  const int tiles = (Rdim + ROWS_PER_ITEM - 1) / ROWS_PER_ITEM;
-  const int total = (*p.n_act) * tiles;
+  unsigned char* ring = smem_raw + (size_t)warp * STAGES * 4 * SEG;
+  uint64_t* full = reinterpret_cast<uint64_t*>(smem_raw + (size_t)S::WARPS * STAGES * 4 * SEG) + warp * STAGES;
 
-  for (int item = blockIdx.x; item < total; item += gridDim.x) {
-    const int e = p.act_list[item / tiles];
-    const int tile = item % tiles;
-    const int slot = st.slot[e];
-    const ExpertPtrs ep = p.experts[slot];
-    const int pos0 = p.offsets[e];
-    const int n = p.offsets[e + 1] - pos0;
-    const int r0 = tile * ROWS_PER_ITEM + warp * RW;
+  const int Kdim = DUAL ? p.H : p.I;
+  const int Rdim = DUAL ? p.I : p.H;
+  const int row_bytes = Kdim * (int)sizeof(T);
+  const int nseg = (row_bytes + SEG - 1) / SEG;
+  const int groups = (Rdim + RW - 1) / RW;
+  const int total_units = (*p.n_act) * groups;
+  const int gw = blockIdx.x * S::WARPS + warp;
+  const int W = gridDim.x * S::WARPS;
+  if (gw >= total_units) return;
 
-    const T* wp[kGemvStreams];
+  if (lane == 0) {
 #pragma unroll
-    for (int s = 0; s < kGemvStreams; ++s) {
-      const int row = min(r0 + (DUAL ? (s & 1) : s), Rdim - 1);
-      const T* base = reinterpret_cast<const T*>(DUAL ? ep.w[s >> 1] : ep.w[2]);
-      wp[s] = base + (size_t)row * Kdim;
-    }
+    for (int i = 0; i < STAGES; ++i) mbar_init(&full[i], 1);
+    mbar_fence_init();
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  __syncwarp();
+  const uint64_t policy = l2_policy_evict_first();
 
-    for (int c0 = 0; c0 < n; c0 += NT) {
-      const int nt = min(NT, n - c0);
+  // what a unit needs: my stream's row pointer (stream = lane & 3), the expert's pair range
+  struct Unit { const unsigned char* row; int pos0, n, r0; };
+  auto load_unit = [&](int u) {
+    Unit q;
+    const int e = p.act_list[u / groups];
+    const ExpertPtrs ep = p.experts[st.slot[e]];
+    q.r0 = (u % groups) * RW;
+    q.pos0 = p.offsets[e];
+    q.n = p.offsets[e + 1] - q.pos0;
+    const int sidx = lane & 3;
+    const int row = min(q.r0 + (DUAL ? (sidx & 1) : sidx), Rdim - 1);
+    const void* base = DUAL ? ep.w[sidx >> 1] : ep.w[2];
+    q.row = reinterpret_cast<const unsigned char*>(base) + (size_t)row * row_bytes;
+    return q;
+  };
+
+  // ---- producer state: runs STAGES-1 stages ahead of the consumer, across unit boundaries ----
+  int pu = gw, ps = 0, issued = 0;
+  Unit pq = load_unit(pu);
+  int p_stages = ((pq.n + NT - 1) / NT) * nseg;
+  auto produce = [&]() {
+    if (pu >= total_units) return;
+    const int slot = issued % STAGES;
+    const int seg = ps % nseg;
+    const uint32_t bytes = (uint32_t)min(SEG, row_bytes - seg * SEG);
+    if (lane == 0) mbar_expect_tx(&full[slot], 4 * bytes);
+    __syncwarp();
+    if (lane < 4) bulk_g2s(ring + (size_t)(slot * 4 + lane) * SEG, pq.row + (size_t)seg * SEG, bytes, &full[slot], policy);
+    ++issued;
+    if (++ps == p_stages) {
+      pu += W;
+      ps = 0;
+      if (pu < total_units) {
+        pq = load_unit(pu);
+        p_stages = ((pq.n + NT - 1) / NT) * nseg;
+      }
+    }
+  };
+#pragma unroll
+  for (int i = 0; i < STAGES - 1; ++i) produce();
+
+  int consumed = 0;
+  bool dead = false;
+  for (int cu = gw; cu < total_units && !dead; cu += W) {
+    const Unit cq = load_unit(cu);
+    for (int c0 = 0; c0 < cq.n && !dead; c0 += NT) {
+      const int nt = min(NT, cq.n - c0);
       const T* xr[NT];
 #pragma unroll
       for (int tt = 0; tt < NT; ++tt) {
-        const int pos = pos0 + c0 + min(tt, nt - 1);
+        const int pos = cq.pos0 + c0 + min(tt, nt - 1);
         if (DUAL) xr[tt] = reinterpret_cast<const T*>(p.x) + (size_t)(p.sorted_pair[pos] / p.K) * p.H;
         else xr[tt] = reinterpret_cast<const T*>(p.h) + (size_t)pos * p.I;
       }
-      float acc[kGemvStreams][NT];
+      float acc[4][NT];
 #pragma unroll
-      for (int s = 0; s < kGemvStreams; ++s)
+      for (int s = 0; s < 4; ++s)
 #pragma unroll
         for (int tt = 0; tt < NT; ++tt) acc[s][tt] = 0.0f;
 
-      Chunk<T> buf[kGemvDepth][kGemvStreams];
-      auto issue = [&](Chunk<T>(&dst)[kGemvStreams], int c) {
-        if (c < nch) {
-#pragma unroll
-          for (int s = 0; s < kGemvStreams; ++s) dst[s].template load<true>(wp[s] + (size_t)c * 8);
+      for (int seg = 0; seg < nseg; ++seg) {
+        produce();
+        const int slot = consumed % STAGES;
+        if (!mbar_wait_bounded(&full[slot], (uint32_t)(consumed / STAGES) & 1u)) {
+          if (lane == 0) atomicOr(status, kDevWaitExpired);
+          dead = true;
+          break;
         }
-      };
-      auto consume = [&](const Chunk<T>(&src)[kGemvStreams], int c) {
-        if (c < nch) {
-          float wf[kGemvStreams][8];
+        ++consumed;
+        constexpr int CB = 8 * (int)sizeof(T);   // bytes of one 8-element chunk
+        const int nchunk = min(SEG, row_bytes - seg * SEG) / CB;
+        const unsigned char* sbase = ring + (size_t)slot * 4 * SEG;
+        for (int cl = lane; cl < nchunk; cl += 32) {
+          float wf[4][8];
 #pragma unroll
-          for (int s = 0; s < kGemvStreams; ++s) src[s].unpack(wf[s]);
+          for (int s = 0; s < 4; ++s) {
+            Chunk<T> wc;
+            wc.from_smem(sbase + (size_t)s * SEG + (size_t)cl * CB);
+            wc.unpack(wf[s]);
+          }
 #pragma unroll
           for (int tt = 0; tt < NT; ++tt) {
             Chunk<T> xc;
-            xc.template load<false>(xr[tt] + (size_t)c * 8);
+            xc.template load<false>(xr[tt] + (size_t)seg * SEG_ELEMS + (size_t)cl * 8);
             float xf[8];
             xc.unpack(xf);
 #pragma unroll
-            for (int s = 0; s < kGemvStreams; ++s)
+            for (int s = 0; s < 4; ++s)
 #pragma unroll
               for (int i = 0; i < 8; ++i) acc[s][tt] = fmaf(wf[s][i], xf[i], acc[s][tt]);
           }
         }
-      };
-#pragma unroll
-      for (int d = 0; d < kGemvDepth - 1; ++d) issue(buf[d], d * 32 + lane);
-      for (int j = 0; j < nj; j += kGemvDepth) {
-#pragma unroll
-        for (int d = 0; d < kGemvDepth; ++d) {
-          issue(buf[(d + kGemvDepth - 1) % kGemvDepth], (j + d + kGemvDepth - 1) * 32 + lane);
-          consume(buf[d], (j + d) * 32 + lane);
-        }
+        __syncwarp();   // every lane is done with the slot before it is refilled
       }
+      if (dead) break;
 
 #pragma unroll
-      for (int s = 0; s < kGemvStreams; ++s)
+      for (int s = 0; s < 4; ++s)
 #pragma unroll
         for (int tt = 0; tt < NT; ++tt) acc[s][tt] = warp_sum(acc[s][tt]);
 
@@ -128,11 +181,12 @@ __global__ void __launch_bounds__(kGemvThreads, 2) ffn_gemv_kernel(FfnParams p, 
         for (int rr = 0; rr < 2; ++rr)
 #pragma unroll
           for (int tt = 0; tt < NT; ++tt) {
-            if (lane == rr * NT + tt && tt < nt && r0 + rr < Rdim) {
+            if (lane == rr * NT + tt && tt < nt && cq.r0 + rr < Rdim) {
+              // stream order is (gate r, gate r+1, up r, up r+1)
               const float g = rn<T>(acc[rr][tt]);
               const float u = rn<T>(acc[2 + rr][tt]);
               const float sg = rn<T>(silu_f32(g));
-              reinterpret_cast<T*>(p.h)[(size_t)(pos0 + c0 + tt) * p.I + r0 + rr] = Elem<T>::from_float(__fmul_rn(sg, u));
+              reinterpret_cast<T*>(p.h)[(size_t)(cq.pos0 + c0 + tt) * p.I + cq.r0 + rr] = Elem<T>::from_float(__fmul_rn(sg, u));
             }
           }
       } else {
@@ -140,8 +194,8 @@ __global__ void __launch_bounds__(kGemvThreads, 2) ffn_gemv_kernel(FfnParams p, 
         for (int rr = 0; rr < 4; ++rr)
 #pragma unroll
           for (int tt = 0; tt < NT; ++tt) {
-            if (lane == rr * NT + tt && tt < nt && r0 + rr < Rdim)
-              reinterpret_cast<T*>(p.y)[(size_t)(pos0 + c0 + tt) * p.H + r0 + rr] = Elem<T>::from_float(acc[rr][tt]);
+            if (lane == rr * NT + tt && tt < nt && cq.r0 + rr < Rdim)
+              reinterpret_cast<T*>(p.y)[(size_t)(cq.pos0 + c0 + tt) * p.H + cq.r0 + rr] = Elem<T>::from_float(acc[rr][tt]);
           }
       }
     }

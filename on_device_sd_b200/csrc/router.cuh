@@ -5,30 +5,28 @@
 // Logit definition.  A logit is the real-number dot product rounded to fp32 and then to the
 // model dtype (the two roundings any fp32-accumulating GEMM applies), plus an optional bias
 // added in the model dtype.  For 16-bit models the kernel evaluates the dot product in fp32
-// and ACCEPTS the result only when its distance to the nearest rounding boundary of the model
-// dtype exceeds a rigorous bound on the fp32 summation error ((H/32+16)*2^-24*|x|*|w|, from
-// the Cauchy-Schwarz bound on sum|x_i w_i|); otherwise the logit is recomputed with fp64
-// accumulation, where products of 16-bit values are exact.  Every logit therefore equals the
-// fp64 definition bit for bit, whatever the summation order.  fp32 models always use fp64
-// accumulation.
+// together with sum|x_i w_i|, and ACCEPTS the fp32 result only when its distance to the nearest
+// rounding boundary of the model dtype exceeds a rigorous bound on the fp32 summation error,
+// (H/128 + 12) * 2^-24 * sum|x_i w_i| (products of 16-bit values are exact in fp32; each of
+// the four accumulators of a lane sees at most H/128 + 2 roundings, then 2 + 5 for the tree).
+// Otherwise the same warp recomputes the logit with fp64 accumulation, where the products are
+// exact and the sum is exact to 2^-53.  Every logit therefore equals the fp64 definition bit
+// for bit, whatever the summation order.  fp32 models always use fp64 accumulation.
 #pragma once
 #include <type_traits>
 #include "common.cuh"
 
 namespace b200moe {
 
-constexpr int kRouterTokensPerTile = 4;   // tokens per CTA tile
 constexpr int kRouterThreads = 256;       // 8 warps = 8 experts per CTA in phase 1
 
 struct RouterParams {
   const void* x;        // [T,H]
   const void* wg;       // [E,H]
   const void* bias;     // [E] or null (model dtype)
-  const float* wnorm2;  // [E] squared row norms of wg
   const void* logits_in;  // [T,E] model dtype (route_from_logits) or null
-  float* logit_sum;     // [T,E] fp32 dot products (workspace)
-  float* xnorm2;        // [T]
-  unsigned* tile_counter;  // [ceil(T/4)], zero between calls
+  float* logits;        // [T,E] final logits (rounded to the model dtype, bias added), as fp32
+  unsigned* tile_counter;  // one per token tile, zero between calls
   int64_t* ids64;       // [T,K]
   void* scores;         // [T,K] model dtype
   unsigned long long* bitmap;  // 4 words or null
@@ -37,15 +35,22 @@ struct RouterParams {
 
 template <typename T> __device__ __forceinline__ double exact_dot(const T* xr, const T* wr, int nch, int lane) {
   double acc = 0.0;
-  for (int c = lane; c < nch; c += 32) {
-    Chunk<T> xc, wc;
-    xc.template load<false>(xr + c * 8);
-    wc.template load<false>(wr + c * 8);
-    float xf[8], wf[8];
-    xc.unpack(xf);
-    wc.unpack(wf);
+  for (int c0 = lane; c0 < nch; c0 += 128) {
+    Chunk<T> xc[4], wc[4];
 #pragma unroll
-    for (int i = 0; i < 8; ++i) acc = fma((double)xf[i], (double)wf[i], acc);
+    for (int u = 0; u < 4; ++u) {
+      const int c = c0 + 32 * u;
+      if (c < nch) { xc[u].template load<false>(xr + c * 8); wc[u].template load<false>(wr + c * 8); }
+      else { xc[u].zero(); wc[u].zero(); }
+    }
+#pragma unroll
+    for (int u = 0; u < 4; ++u) {
+      float xf[8], wf[8];
+      xc[u].unpack(xf);
+      wc[u].unpack(wf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) acc = fma((double)xf[i], (double)wf[i], acc);
+    }
   }
   return warp_sum(acc);
 }
@@ -74,49 +79,16 @@ __device__ void topk_softmax_token(const RouterParams& p, int t, int lane, float
   const int E = p.E, K = p.K;
   const int nj = (E + 31) / 32;
   float v[kMaxJ];
-  const T* bias = reinterpret_cast<const T*>(p.bias);
-
-  if (p.logits_in != nullptr) {
-    const T* lg = reinterpret_cast<const T*>(p.logits_in) + (size_t)t * E;
 #pragma unroll
-    for (int j = 0; j < kMaxJ; ++j) {
-      const int e = j * 32 + lane;
-      v[j] = (j < nj && e < E) ? Elem<T>::to_float(lg[e]) : -INFINITY;
-    }
-  } else {
-    const int nch = p.H / 8;
-    const T* xr = reinterpret_cast<const T*>(p.x) + (size_t)t * p.H;
-    const float xn = __ldcg(p.xnorm2 + t);
-    const float cH = (float)(p.H / 32 + 16) * 5.9604645e-8f * 1.01f;
-#pragma unroll
-    for (int j = 0; j < kMaxJ; ++j) {
-      if (j >= nj) { v[j] = -INFINITY; continue; }   // uniform across the warp
-      const int e = j * 32 + lane;
-      float s = 0.0f;
-      bool risky = false;
-      if (e < E) {
-        s = __ldcg(p.logit_sum + (size_t)t * E + e);
-        if (!std::is_same<T, float>::value) {
-          const float bound = cH * sqrtf(xn * p.wnorm2[e]) + 1e-37f;
-          risky = !(boundary_distance<T>(s) > bound);
-        }
-      }
-      unsigned m = __ballot_sync(0xffffffffu, risky);
-      while (m) {
-        const int src = __ffs(m) - 1;
-        m &= m - 1;
-        const int e2 = j * 32 + src;
-        const double d = exact_dot<T>(xr, reinterpret_cast<const T*>(p.wg) + (size_t)e2 * p.H, nch, lane);
-        if (lane == src) s = (float)d;
-      }
-      float l = rn<T>(s);
-      if (bias != nullptr && e < E) l = rn<T>(l + Elem<T>::to_float(bias[e]));
-      v[j] = (e < E) ? l : -INFINITY;
-      // keep the final logit where b200moe_last_logits can read it back
-      if (e < E) p.logit_sum[(size_t)t * E + e] = l;
+  for (int j = 0; j < kMaxJ; ++j) {
+    const int e = j * 32 + lane;
+    if (j < nj && e < E) {
+      v[j] = p.logits_in != nullptr ? Elem<T>::to_float(reinterpret_cast<const T*>(p.logits_in)[(size_t)t * E + e])
+                                    : __ldcg(p.logits + (size_t)t * E + e);
+    } else {
+      v[j] = -INFINITY;
     }
   }
-
   // ---- selection: k rounds of (max value, lowest index) ----
   unsigned taken = 0;
   float kth = 0.0f;
@@ -197,11 +169,12 @@ __device__ void topk_softmax_token(const RouterParams& p, int t, int lane, float
   }
 }
 
-// grid = (ceil(T/4), ceil(E/8)), 256 threads.  Phase 1: warp w of CTA (bx,by) computes the dot
-// products of expert by*8+w with the 4 tokens of tile bx.  The CTA that finishes a tile last
-// runs phase 2 (top-k) for its tokens; the counter returns to zero for the next call.
-template <typename T> __global__ void __launch_bounds__(kRouterThreads) router_kernel(RouterParams p) {
-  constexpr int TT = kRouterTokensPerTile;
+// grid = (ceil(T/TT), ceil(E/8)), 256 threads.  Phase 1: warp w of CTA (bx,by) computes the
+// logits of expert by*8+w for the TT tokens of tile bx and certifies (or recomputes) each.
+// The CTA that finishes a tile last runs phase 2 (top-k) for its tokens; the counter returns to
+// zero for the next call.  TT = 1 with 8 chunk positions per trip serves small batches
+// (latency-bound: every load of a row is in flight at once); TT = 4 amortises the weight row.
+template <typename T, int TT, int U> __global__ void __launch_bounds__(kRouterThreads) router_kernel(RouterParams p) {
   constexpr bool kExact = std::is_same<T, float>::value;
   using Acc = typename std::conditional<kExact, double, float>::type;
   __shared__ float skey[TT][32];
@@ -212,17 +185,18 @@ template <typename T> __global__ void __launch_bounds__(kRouterThreads) router_k
   const int e = blockIdx.y * (kRouterThreads / 32) + warp;
   const int nch = p.H / 8;
   const T* x = reinterpret_cast<const T*>(p.x);
+  const T* bias = reinterpret_cast<const T*>(p.bias);
 
   if (e < p.E) {
     const T* wrow = reinterpret_cast<const T*>(p.wg) + (size_t)e * p.H;
-    const bool do_norm = (blockIdx.y == 0 && warp == 0);
-    Acc acc[TT];
-    float xn[TT];
+    Acc acc[TT][4];
+    float sabs[TT];
 #pragma unroll
-    for (int tt = 0; tt < TT; ++tt) { acc[tt] = 0; xn[tt] = 0.0f; }
-    // two chunk positions per trip, all ten loads issued before the first use: the loop is
-    // latency-bound (a warp owns one expert row), so loads in flight are what matter
-    constexpr int U = 2;
+    for (int tt = 0; tt < TT; ++tt) {
+      sabs[tt] = 0.0f;
+#pragma unroll
+      for (int a = 0; a < 4; ++a) acc[tt][a] = 0;
+    }
     for (int c0 = lane; c0 < nch; c0 += 32 * U) {
       Chunk<T> wc[U], xc[U][TT];
 #pragma unroll
@@ -249,21 +223,30 @@ template <typename T> __global__ void __launch_bounds__(kRouterThreads) router_k
           xc[u][tt].unpack(xf);
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
-            if (kExact) acc[tt] = fma((double)xf[i], (double)wf[i], acc[tt]);
-            else acc[tt] = fmaf(xf[i], wf[i], acc[tt]);
-            if (do_norm) xn[tt] = fmaf(xf[i], xf[i], xn[tt]);
+            if (kExact) {
+              acc[tt][i & 3] = fma((double)xf[i], (double)wf[i], acc[tt][i & 3]);
+            } else {
+              acc[tt][i & 3] = fmaf(xf[i], wf[i], acc[tt][i & 3]);
+              sabs[tt] = fmaf(fabsf(xf[i]), fabsf(wf[i]), sabs[tt]);
+            }
           }
         }
       }
     }
+    const float cH = (float)(p.H / 128 + 12) * 5.9604645e-8f * 1.01f;
 #pragma unroll
     for (int tt = 0; tt < TT; ++tt) {
-      const Acc s = warp_sum(acc[tt]);
-      if (lane == 0 && t0 + tt < p.T) p.logit_sum[(size_t)(t0 + tt) * p.E + e] = (float)s;
-      if (do_norm) {
-        const float n2 = warp_sum(xn[tt]);
-        if (lane == 0 && t0 + tt < p.T) p.xnorm2[t0 + tt] = n2;
+      const Acc part = (acc[tt][0] + acc[tt][1]) + (acc[tt][2] + acc[tt][3]);
+      float s = (float)warp_sum(part);
+      if (!kExact) {
+        const float bound = cH * warp_sum(sabs[tt]) + 1e-37f;
+        const bool risky = !(boundary_distance<T>(s) > bound);    // uniform: every lane holds the same sums
+        if (risky && t0 + tt < p.T)
+          s = (float)exact_dot<T>(x + (size_t)(t0 + tt) * p.H, wrow, nch, lane);
       }
+      float l = rn<T>(s);
+      if (bias != nullptr) l = rn<T>(l + Elem<T>::to_float(bias[e]));
+      if (lane == 0 && t0 + tt < p.T) p.logits[(size_t)(t0 + tt) * p.E + e] = l;
     }
   }
   __threadfence();
@@ -286,23 +269,6 @@ template <typename T> __global__ void __launch_bounds__(kRouterThreads) router_f
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * (kRouterThreads / 32) + warp;
   if (t < p.T) topk_softmax_token<T>(p, t, lane, skey[warp], sidx[warp]);
-}
-
-// Squared row norms of the gate weight, one warp per expert (set_gate).
-template <typename T> __global__ void gate_norm_kernel(const T* wg, float* wnorm2, int E, int H) {
-  const int warp = (blockIdx.x * blockDim.x + threadIdx.x) >> 5, lane = threadIdx.x & 31;
-  if (warp >= E) return;
-  float acc = 0.0f;
-  for (int c = lane; c < H / 8; c += 32) {
-    Chunk<T> wc;
-    wc.template load<false>(wg + (size_t)warp * H + c * 8);
-    float wf[8];
-    wc.unpack(wf);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) acc = fmaf(wf[i], wf[i], acc);
-  }
-  acc = warp_sum(acc);
-  if (lane == 0) wnorm2[warp] = acc;
 }
 
 }  // namespace b200moe

@@ -211,3 +211,54 @@ def test_full_size_against_device_run_of_oracle(name, T):
         a = ctx.forward(0, L.x, ids, scores, expert_slot=half).float()
         b = ctx.forward(0, L.x, ids, scores, expert_slot=other).float()
         assert O.mean_rel((a + b).to(L.dtype), out) <= 5e-3
+
+
+# ---------------------------------------------------------------------------------------------
+# kernel families: the CUDA-core GEMV path and the tcgen05 tensor-core path must agree with the
+# oracle on the same inputs, whatever the per-expert token count
+# ---------------------------------------------------------------------------------------------
+def _kinds():
+    from on_device_sd_b200 import FFN_GEMV, FFN_MMA
+    return {"gemv": FFN_GEMV, "mma": FFN_MMA}
+
+
+@pytest.mark.parametrize("kind", ["gemv", "mma"])
+@pytest.mark.parametrize("T", [1, 3, 16, 17, 40])
+def test_kernel_families_small_bf16(kind, T):
+    from on_device_sd_b200.synth import make_layer
+    H, E, K, I = 256, 16, 4, 192          # I is not a multiple of the 64-row tile of the tensor-core kernel
+    L = make_layer(H, E, K, I, torch.bfloat16, T, seed=11)
+    ctx = _ctx(H, E, K, I, torch.bfloat16, max_tokens=64)
+    ctx.set_gate(0, L.gate_w.cuda())
+    _register(ctx, L.experts)
+    out, ids, scores = ctx.forward_fused(0, L.x.cuda(), return_routing=True, ffn_kind=_kinds()[kind])
+    assert ctx.status() == 0
+    want = O.moe_engine(L.x, ids.cpu(), scores.cpu(), L.experts, order=sorted(set(ids.flatten().tolist())))
+    _close(out, want, torch.bfloat16, tight=True)
+
+
+@pytest.mark.parametrize("kind", ["gemv", "mma"])
+def test_kernel_families_many_tokens_one_expert(kind):
+    """200 tokens all routed to the same two experts: more than one pass of 128 tokens in the
+    tensor-core kernel, 50 passes of 4 in the GEMV kernel; K = 328 is not a multiple of 64."""
+    from on_device_sd_b200.synth import make_layer
+    H, E, K, I, T = 328, 4, 2, 136, 200
+    L = make_layer(H, E, K, I, torch.bfloat16, T, seed=12)
+    ctx = _ctx(H, E, K, I, torch.bfloat16, max_tokens=256)
+    _register(ctx, L.experts)
+    ids = torch.tensor([[3, 1]] * T)
+    sc = torch.softmax(torch.randn(T, K, generator=torch.Generator().manual_seed(2)), -1).bfloat16()
+    out = ctx.forward(0, L.x.cuda(), ids.cuda(), sc.cuda(), ffn_kind=_kinds()[kind])
+    assert ctx.status() == 0
+    _close(out, O.moe_engine(L.x, ids, sc, L.experts, order=[1, 3]), torch.bfloat16, tight=True)
+
+
+def test_expert_ffn_tensor_core_path():
+    from on_device_sd_b200 import expert_forward_with_weights
+    g = torch.Generator().manual_seed(3)
+    H, I, n = 512, 320, 48
+    x = torch.randn(n, H, generator=g).bfloat16()
+    p = {"gate_proj": (torch.randn(I, H, generator=g) * 0.02).bfloat16(), "up_proj": (torch.randn(I, H, generator=g) * 0.02).bfloat16(),
+         "down_proj": (torch.randn(H, I, generator=g) * 0.02).bfloat16()}
+    out = expert_forward_with_weights(x.cuda(), p["gate_proj"].cuda(), p["up_proj"].cuda(), p["down_proj"].cuda())
+    _close(out, O.expert_ffn(x, **p), torch.bfloat16, tight=True)
