@@ -209,7 +209,9 @@ def run_ours(args, workload):
     int4 = wmode == "int4"
     L = make_named(cfg_name, 1, seed=rank, device=dev, gen_device="cuda")
     shape = MoEShape(H, E, K, I, "bfloat16")
-    runner = B200MoERunner(shape, device=dev, max_tokens=max(batches), weight_mode=W_INT4_G128 if int4 else W_DENSE)
+    from on_device_sd_b200 import FFN_AUTO, FFN_GEMV, FFN_MMA
+    kind = {"auto": FFN_AUTO, "gemv": FFN_GEMV, "mma": FFN_MMA}[args.ffn_kind]
+    runner = B200MoERunner(shape, device=dev, max_tokens=max(batches), weight_mode=W_INT4_G128 if int4 else W_DENSE, ffn_kind=kind)
     runner.load_gate(0, L.gate_w)
     dense_experts = L.experts
     if int4:
@@ -221,9 +223,25 @@ def run_ours(args, workload):
     outs = {T: torch.empty_like(xs[T]) for T in batches}
     ctx = runner.ctx
 
-    def step():
+    def step_eager():
         for T in batches:
-            ctx.forward_fused(0, xs[T], out=outs[T])
+            ctx.forward_fused(0, xs[T], out=outs[T], ffn_kind=kind)
+
+    def capture(fn):
+        """One step as a CUDA graph (the calls enqueue kernels only, so they capture as they are)."""
+        if args.no_graph:
+            return None
+        try:
+            fn(); torch.cuda.synchronize()
+            g = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g):
+                fn()
+            g.replay(); torch.cuda.synchronize()
+            return g
+        except Exception as exc:  # noqa: BLE001
+            print(f"[bench] CUDA graph capture failed ({exc}); timing eager launches", file=sys.stderr)
+            torch.cuda.synchronize()
+            return None
 
     # distinct experts selected per batch (for the algorithmic byte count)
     n_active = {}
@@ -232,6 +250,12 @@ def run_ours(args, workload):
         n_active[T] = int(ids.unique().numel())
     ctx.status()
 
+    graph = capture(step_eager)
+    step = graph.replay if graph is not None else step_eager
+    launches_per_step = None
+    l_before = ctx.launches
+    step_eager(); torch.cuda.synchronize()
+    launches_per_step = ctx.launches - l_before
     for _ in range(max(args.warmup, 3)):
         step()
     torch.cuda.synchronize()
@@ -254,7 +278,7 @@ def run_ours(args, workload):
     if world > 1:
         dist.barrier()
     ms = ev0.elapsed_time(ev1)
-    launches = ctx.launches - l0
+    launches = (ctx.launches - l0) if graph is None else launches_per_step * args.steps
     if world > 1:
         t = torch.tensor([ms], device=dev)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
@@ -274,7 +298,7 @@ def run_ours(args, workload):
     # per-kernel CUDA-event durations: the same steps again with every launch bracketed by events
     ctx.profile(True)
     for _ in range(args.steps):
-        step()
+        step_eager()
     torch.cuda.synchronize()
     ctx.profile(False)
     prof = ctx.profile_read()
@@ -342,22 +366,32 @@ def run_ours(args, workload):
 
     per_T = {}
     for T in batches:   # short individual timings, reported for context only
+        one = lambda T=T: ctx.forward_fused(0, xs[T], out=outs[T], ffn_kind=kind)
+        gT = capture(one)
+        runT = gT.replay if gT is not None else one
         a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
         a.record()
         for _ in range(20):
-            ctx.forward_fused(0, xs[T], out=outs[T])
+            runT()
         b.record(); torch.cuda.synchronize()
         us = a.elapsed_time(b) / 20 * 1e3
         lb = algorithmic_bytes(H, E, I, T, n_active[T], int4)[0]
+        ctx.profile(True)
+        for _ in range(10):
+            ctx.forward_fused(0, xs[T], out=outs[T], ffn_kind=kind)
+        torch.cuda.synchronize()
+        ctx.profile(False)
+        kp = {k: round(v[0] / max(v[1], 1) * 1e3, 1) for k, v in ctx.profile_read().items()}
         per_T[str(T)] = {"us": round(us, 1), "tokens_per_s": round(T / us * 1e6), "experts_hit": n_active[T],
-                         "layer_gbs": round(lb / us / 1e3, 1), "frac_of_peak": round(lb / us / 1e3 / peak, 3)}
+                         "layer_gbs": round(lb / us / 1e3, 1), "frac_of_peak": round(lb / us / 1e3 / peak, 3), "kernel_us": kp}
 
     line = {
         "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": max(args.warmup, 3),
         "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": workload, "layer": cfg_name, "hidden": H, "experts": E, "top_k": K, "intermediate": I,
-                   "token_batches": list(batches), "weights": wmode, "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
+                   "token_batches": list(batches), "weights": wmode, "ffn_kind": args.ffn_kind,
+                   "launch": "one CUDA graph replay per step" if graph is not None else "eager launches", "parallelism": "single GPU" if world == 1 else f"{world} independent replicas",
                    "l2": "expert weights of one step (0.7-2.8 GB for mixtral) exceed the 126 MB L2, no flush needed" if cfg_name == "mixtral"
                          else "weights of the larger batches exceed L2; the smallest batches can be L2-resident"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": tokens_per_step * H * 2, "d2h_bytes_per_step": tokens_per_step * H * 2,
@@ -378,6 +412,8 @@ def main():
     ap.add_argument("--workload", default="mixtral_bf16", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batches", default=None, help="comma-separated token batches replacing the workload's sweep (profiling runs)")
+    ap.add_argument("--ffn-kind", default="auto", choices=["auto", "gemv", "mma"], help="force one expert-FFN kernel family")
+    ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
     ap.add_argument("--quick", action="store_true", help="timed region only: no e2e, per-T or CPU-baseline legs (for ncu captures)")
     args = ap.parse_args()
     if args.batches:

@@ -372,8 +372,8 @@ static int route_common(b200moe_ctx* ctx, int layer, const void* x, const void* 
   int rc = check_layer(ctx, layer, who);
   if (rc) return rc;
   if ((rc = check_tokens(ctx, T, who))) return rc;
-  if (!ids_out || !scores_out || (!x && !logits)) return fail(ctx, B200MOE_E_ARG, "%s: null pointer", who);
-  if (!logits && !ctx->gate_w[layer]) return fail(ctx, B200MOE_E_STATE, "%s: no gate weight registered for layer %d", who, layer);
+  if (T > 0 && (!ids_out || !scores_out || (!x && !logits))) return fail(ctx, B200MOE_E_ARG, "%s: null pointer", who);
+  if (!logits && x && !ctx->gate_w[layer]) return fail(ctx, B200MOE_E_STATE, "%s: no gate weight registered for layer %d", who, layer);
   if (x && misaligned(x)) return fail(ctx, B200MOE_E_ARG, "%s: x must be 16-byte aligned", who);
   CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -390,13 +390,13 @@ static int route_common(b200moe_ctx* ctx, int layer, const void* x, const void* 
 
 extern "C" int b200moe_route(b200moe_ctx* ctx, int layer, const void* x, int T, int64_t* ids_out, void* scores_out,
                              uint64_t* active_bitmap_out, void* stream) {
-  if (!x) return fail(ctx, B200MOE_E_ARG, "b200moe_route: null x");
+  if (!x && T > 0) return fail(ctx, B200MOE_E_ARG, "b200moe_route: null x");
   return route_common(ctx, layer, x, nullptr, T, ids_out, scores_out, active_bitmap_out, stream, "b200moe_route");
 }
 
 extern "C" int b200moe_route_from_logits(b200moe_ctx* ctx, const void* logits, int T, int64_t* ids_out, void* scores_out,
                                          uint64_t* active_bitmap_out, void* stream) {
-  if (!logits) return fail(ctx, B200MOE_E_ARG, "b200moe_route_from_logits: null logits");
+  if (!logits && T > 0) return fail(ctx, B200MOE_E_ARG, "b200moe_route_from_logits: null logits");
   return route_common(ctx, 0, nullptr, logits, T, ids_out, scores_out, active_bitmap_out, stream, "b200moe_route_from_logits");
 }
 
@@ -502,6 +502,8 @@ template <int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, const UmmaPara
   return post_launch(ctx, "ffn_umma_kernel<down>");
 }
 
+// max_n bounds the tokens any expert can hold in this call (the batch size); a pass of the
+// kernel covers NMAX tokens, so larger per-expert counts only cost extra passes.
 static int launch_ffn_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tmaps, const SlotTable& st, int max_n, cudaStream_t s) {
   if (!tmaps) return fail(ctx, B200MOE_E_UNSUPPORTED, "tensor-core path unavailable: no TMA descriptors for these experts");
   UmmaParams up{};
@@ -529,7 +531,7 @@ static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st,
 #endif
   }
 #ifdef B200MOE_WITH_UMMA
-  if (c.act_dtype == B200MOE_BF16 && ffn_kind != B200MOE_FFN_GEMV && (ffn_kind == B200MOE_FFN_MMA || f.max_n > 4)) {
+  if (c.act_dtype == B200MOE_BF16 && ffn_kind != B200MOE_FFN_GEMV && (ffn_kind == B200MOE_FFN_MMA || f.max_n > 1)) {
     int rc = launch_ffn_umma(ctx, p, f.tmaps, st, f.max_n, s);
     if (rc != B200MOE_E_UNSUPPORTED) return rc;
     if (ffn_kind == B200MOE_FFN_MMA) return rc;
@@ -665,7 +667,7 @@ extern "C" int b200moe_expert_ffn(b200moe_ctx* ctx, const void* x, int n, const 
   f.experts = slot; f.offsets = ctx->one_offsets; f.sorted_pair = ctx->one_sorted; f.act_list = ctx->one_act; f.n_act = ctx->one_nact;
   f.x = x; f.h = ctx->h; f.y = out; f.K = 1; f.max_n = n;
 #ifdef B200MOE_WITH_UMMA
-  if (!ctx->h_tmaps.empty() && n > 4) {
+  if (!ctx->h_tmaps.empty() && n > 1) {
     const size_t idx = (size_t)c.num_layers * c.num_experts;
     if (encode_expert_maps(ctx, &ctx->h_tmaps[idx * 3], gate_proj, up_proj, down_proj)) {
       CUDA_TRY(ctx, cudaMemcpyAsync(ctx->d_tmaps + idx * 3, &ctx->h_tmaps[idx * 3], 3 * sizeof(CUtensorMap), cudaMemcpyHostToDevice, st));

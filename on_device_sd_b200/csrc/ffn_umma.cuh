@@ -10,8 +10,8 @@
 //
 //   warp 0     TMA producer (one elected lane): weight tiles -> shared-memory ring
 //   warp 1     MMA issuer (one elected lane) + owner of the TMEM allocation
-//   warps 2-3  token-tile loaders (cp.async gather of x rows / h rows)
-//   warps 4-7  epilogue: tcgen05.ld, rounding points, SwiGLU, stores (overlaps the next tile's
+//   warps 2-5  token-tile loaders (cp.async gather of x rows / h rows)
+//   warps 6-9  epilogue: tcgen05.ld, rounding points, SwiGLU, stores (overlaps the next tile's
 //              main loop through a double-buffered accumulator)
 //
 // DUAL  (gate/up): one tile = 64 rows of gate_proj stacked on the same 64 rows of up_proj, so one
@@ -30,16 +30,20 @@
 
 namespace b200moe {
 
-constexpr int kUmmaThreads = 256;
+constexpr int kUmmaThreads = 320;
+constexpr int kUmmaLoaders = 128;        // threads gathering token tiles
 constexpr int kUmmaBK = 64;          // k elements per stage (128 bytes of bf16)
 constexpr int kUmmaATile = 16384;    // 128 rows x 128 bytes
 
+// NMAX = tokens per pass (the widest MMA N) sizes the token tile of a stage and the TMEM
+// allocation; whatever shared memory is left goes to ring depth.
 template <int NMAX> struct UmmaShape {
   static constexpr int B_TILE = NMAX * 128;
   static constexpr int STAGE = kUmmaATile + B_TILE;
   static constexpr int STAGES = (200 * 1024 / STAGE) > 12 ? 12 : (200 * 1024 / STAGE);
   static constexpr int EX_BYTES = 64 * 17 * 4;
-  static constexpr size_t SMEM = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE + EX_BYTES + (2 * STAGES + 4) * 8 + 64;
+  static constexpr int PTR_BYTES = 128 * 8;
+  static constexpr size_t SMEM = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE + EX_BYTES + PTR_BYTES + (2 * STAGES + 4) * 8 + 64;
   static constexpr int TMEM_COLS = (2 * NMAX) < 32 ? 32 : 2 * NMAX;
 };
 
@@ -115,6 +119,7 @@ template <int NMAX, bool DUAL>
 __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up, SlotTable st) {
   using S = UmmaShape<NMAX>;
   constexpr int STAGES = S::STAGES;
+  constexpr int B_TILE = S::B_TILE;
   constexpr int TILE_ROWS = DUAL ? 64 : 128;       // output rows per tile
   constexpr int LOADER_LAG = 2;                    // cp.async groups a loader keeps in flight
   static_assert(STAGES > LOADER_LAG + 1, "ring too shallow");
@@ -123,8 +128,9 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   unsigned char* As = smem;
   unsigned char* Bs = smem + (size_t)STAGES * kUmmaATile;
-  float* ex = reinterpret_cast<float*>(Bs + (size_t)STAGES * S::B_TILE);
-  uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ex) + S::EX_BYTES);
+  float* ex = reinterpret_cast<float*>(Bs + (size_t)STAGES * B_TILE);
+  const __nv_bfloat16** rowptr = reinterpret_cast<const __nv_bfloat16**>(reinterpret_cast<unsigned char*>(ex) + S::EX_BYTES);
+  uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(rowptr) + S::PTR_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
   uint64_t* acc_empty = acc_full + 2;
@@ -139,7 +145,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   const int total = (*p.n_act) * tiles;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1 + 64); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1 + kUmmaLoaders); mbar_init(&empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
     *abort_flag = 0;
     mbar_fence_init();
@@ -158,7 +164,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
     // ------------------------------ TMA producer ------------------------------
     if (lane == 0) {
       const uint64_t policy = l2_policy_evict_first();
-      int it = 0;
+      int s = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
         const int e = p.act_list[item / tiles];
@@ -170,9 +177,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
         tensormap_acquire(m0);
         if (DUAL) tensormap_acquire(m1);
         for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
-          for (int kb = 0; kb < nkb; ++kb, ++it) {
-            const int s = it % STAGES;
-            if (!wait_or_abort(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
+          for (int kb = 0; kb < nkb; ++kb) {
+            if (!wait_or_abort(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
             mbar_expect_tx(&full[s], kUmmaATile);
             unsigned char* dst = As + (size_t)s * kUmmaATile;
             if (DUAL) {
@@ -181,6 +187,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
             } else {
               tma_load_2d(dst, m0, kb * kUmmaBK, tile * 128, &full[s], policy);
             }
+            if (++s == STAGES) { s = 0; ph ^= 1; }
           }
         }
       }
@@ -189,7 +196,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   } else if (warp == 1) {
     // ------------------------------ MMA issuer ------------------------------
     if (lane == 0) {
-      int it = 0, job = 0;
+      int s = 0, job = 0;
+      uint32_t ph = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
         const int e = p.act_list[item / tiles];
@@ -201,76 +209,76 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
           if (!wait_or_abort(&acc_empty[b], ((job >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(b * NMAX);
-          for (int kb = 0; kb < nkb; ++kb, ++it) {
-            const int s = it % STAGES;
-            if (!wait_or_abort(&full[s], (it / STAGES) & 1, abort_flag)) { ok = false; break; }
+          for (int kb = 0; kb < nkb; ++kb) {
+            if (!wait_or_abort(&full[s], ph, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint64_t adesc = umma_desc_sw128(smem_addr(As + (size_t)s * kUmmaATile));
-            const uint64_t bdesc = umma_desc_sw128(smem_addr(Bs + (size_t)s * S::B_TILE));
+            const uint64_t bdesc = umma_desc_sw128(smem_addr(Bs + (size_t)s * B_TILE));
 #pragma unroll
             for (int k = 0; k < kUmmaBK / 16; ++k)   // 32 bytes of K per instruction: +2 in the 16-byte address field
               tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
             tc_commit(&empty[s]);      // frees the stage when these MMAs have read it
+            if (++s == STAGES) { s = 0; ph ^= 1; }
           }
           if (ok) tc_commit(&acc_full[b]);
         }
       }
       if (!ok) atomicOr(up.status, kDevWaitExpired);
     }
-  } else if (warp < 4) {
+  } else if (warp < 6) {
     // ------------------------------ token-tile loaders ------------------------------
-    const int tl = threadIdx.x - 64;          // 0..63
-    const int chunk = tl & 7;                 // 16-byte chunk of the 128-byte row
-    const int rbase = tl >> 3;                // rows rbase, rbase+8, ...
-    int it = 0;
+    const int tl = threadIdx.x - 64;          // 0..127
+    int s = 0, lag_s = 0, issued = 0;         // stage being filled; oldest stage not yet signalled
+    uint32_t ph = 0;
     bool ok = true;
-    int issued = 0;                           // stages this thread has issued copies for
-    for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+    for (int item = blockIdx.x; item < total; item += gridDim.x) {   // runs to the end even after a failed wait: the named barriers below need all 128 threads
       const int e = p.act_list[item / tiles];
       const int pos0 = p.offsets[e];
       const int n = p.offsets[e + 1] - pos0;
-      for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
+      for (int c0 = 0; c0 < n; c0 += NMAX) {
         const int nt = min(NMAX, n - c0);
         const int npad = (nt + 15) & ~15;
-        const __nv_bfloat16* rows[NMAX / 8];
-#pragma unroll
-        for (int j = 0; j < NMAX / 8; ++j) {
-          const int r = rbase + 8 * j;
-          const int pos = pos0 + c0 + min(r, nt - 1);
-          if (DUAL) rows[j] = reinterpret_cast<const __nv_bfloat16*>(p.x) + (size_t)(p.sorted_pair[pos] / p.K) * p.H;
-          else rows[j] = reinterpret_cast<const __nv_bfloat16*>(p.h) + (size_t)pos * p.I;
+        // row pointers of this pass, shared by the loader threads
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        if (tl < npad) {
+          const int pos = pos0 + c0 + min(tl, nt - 1);
+          rowptr[tl] = DUAL ? reinterpret_cast<const __nv_bfloat16*>(p.x) + (size_t)(p.sorted_pair[pos] / p.K) * p.H
+                            : reinterpret_cast<const __nv_bfloat16*>(p.h) + (size_t)pos * p.I;
         }
-        for (int kb = 0; kb < nkb; ++kb, ++it) {
-          const int s = it % STAGES;
-          if (!wait_or_abort(&empty[s], ((it / STAGES) & 1) ^ 1, abort_flag)) { ok = false; break; }
-          unsigned char* bt = Bs + (size_t)s * S::B_TILE;
-          const int k0 = kb * kUmmaBK + chunk * 8;
-#pragma unroll
-          for (int j = 0; j < NMAX / 8; ++j) {
-            const int r = rbase + 8 * j;
-            if (r < npad) {
-              const bool live = (r < nt) && (k0 < Kdim);
-              cp_async_16(bt + r * 128 + ((chunk ^ (r & 7)) << 4), live ? (const void*)(rows[j] + k0) : (const void*)rows[j], live ? 16u : 0u);
-            }
+        asm volatile("bar.sync 2, 128;" ::: "memory");
+        for (int kb = 0; kb < nkb && ok; ++kb) {
+          if (!wait_or_abort(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          unsigned char* bt = Bs + (size_t)s * B_TILE;
+          for (int id = tl; id < npad * 8; id += kUmmaLoaders) {
+            const int r = id >> 3, chunk = id & 7;
+            const int k0 = kb * kUmmaBK + chunk * 8;
+            const bool live = (r < nt) && (k0 < Kdim);
+            const __nv_bfloat16* src = rowptr[r];
+            cp_async_16(bt + r * 128 + ((chunk ^ (r & 7)) << 4), live ? (const void*)(src + k0) : (const void*)src, live ? 16u : 0u);
           }
           cp_async_commit();
           ++issued;
           if (issued > LOADER_LAG) {              // the group issued LOADER_LAG stages ago has landed
             cp_async_wait<LOADER_LAG>();
             fence_proxy_async();
-            mbar_arrive(&full[(it - LOADER_LAG) % STAGES]);
+            mbar_arrive(&full[lag_s]);
+            if (++lag_s == STAGES) lag_s = 0;
           }
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
       }
     }
     cp_async_wait<0>();
     fence_proxy_async();
-    for (int q = min(issued, LOADER_LAG); q > 0; --q) mbar_arrive(&full[(it - q) % STAGES]);
+    for (int q = min(issued, LOADER_LAG); q > 0; --q) {
+      mbar_arrive(&full[lag_s]);
+      if (++lag_s == STAGES) lag_s = 0;
+    }
     if (!ok && tl == 0) atomicOr(up.status, kDevWaitExpired);
   } else {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;                       // TMEM lane quarter this warp may read
-    const int et = threadIdx.x - 128;             // 0..127
+    const int et = threadIdx.x - 192;             // 0..127
     int job = 0;
     bool ok = true;
     __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h);
