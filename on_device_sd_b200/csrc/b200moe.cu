@@ -9,8 +9,10 @@
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <algorithm>
 #include <new>
 #include <string>
+#include <utility>
 #include <vector>
 
 #include "common.cuh"
@@ -105,6 +107,24 @@ static int fail(b200moe_ctx* ctx, int code, const char* fmt, ...) {
     if (e_ != cudaSuccess)                                                                         \
       return fail(ctx, B200MOE_E_CUDA, "%s failed: %s (%s:%d)", #call, cudaGetErrorString(e_), __FILE__, __LINE__); \
   } while (0)
+
+// Launch with the programmatic-stream-serialization attribute: the kernel may begin while its
+// predecessor in the stream is still running and synchronises on the device (pdl_wait).
+static bool g_use_pdl = getenv("B200MOE_NO_PDL") == nullptr;
+template <typename... KArgs, typename... Args>
+static void launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.dynamicSmemBytes = smem;
+  cfg.stream = s;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);   // errors surface in post_launch
+}
 
 static size_t elem_bytes(int dtype) { return dtype == B200MOE_F32 ? 4 : 2; }
 
@@ -354,14 +374,14 @@ static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void*
     using Tt = decltype(tag);
     ProfScope prof(ctx, B200MOE_KERNEL_ROUTER, st);
     if (logits) {
-      router_from_logits_kernel<Tt><<<(T + 7) / 8, kRouterThreads, 0, st>>>(p);
+      launch_chain(router_from_logits_kernel<Tt>, dim3((T + 7) / 8), dim3(kRouterThreads), 0, st, p);
       return post_launch(ctx, "router_from_logits_kernel");
     }
     const unsigned ey = (c.num_experts + 7) / 8;
     if ((long long)T * ey <= 2LL * ctx->sm_count) {   // small batch: one token per tile, deep unroll
-      router_kernel<Tt, 1, 8><<<dim3(T, ey), kRouterThreads, 0, st>>>(p);
+      launch_chain(router_kernel<Tt, 1, 8>, dim3(T, ey), dim3(kRouterThreads), 0, st, p);
     } else {
-      router_kernel<Tt, 4, 2><<<dim3((T + 3) / 4, ey), kRouterThreads, 0, st>>>(p);
+      launch_chain(router_kernel<Tt, 4, 2>, dim3((T + 3) / 4, ey), dim3(kRouterThreads), 0, st, p);
     }
     return post_launch(ctx, "router_kernel");
   });
@@ -457,13 +477,13 @@ template <typename T, int NT, typename S> static int launch_gemv_pair_shape(b200
   }
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
-    up<<<grid, S::THREADS, S::SMEM, s>>>(p, st, ctx->status);
+    launch_chain(up, dim3(grid), dim3(S::THREADS), S::SMEM, s, p, st, ctx->status);
   }
   int rc = post_launch(ctx, "ffn_gemv_kernel<gate/up>");
   if (rc) return rc;
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_DOWN, s);
-    down<<<grid, S::THREADS, S::SMEM, s>>>(p, st, ctx->status);
+    launch_chain(down, dim3(grid), dim3(S::THREADS), S::SMEM, s, p, st, ctx->status);
   }
   return post_launch(ctx, "ffn_gemv_kernel<down>");
 }
@@ -491,13 +511,13 @@ template <int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, const UmmaPara
   }
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
-    k_up<<<ctx->sm_count, kUmmaThreads, S::SMEM, s>>>(up, st);
+    launch_chain(k_up, dim3(ctx->sm_count), dim3(kUmmaThreads), S::SMEM, s, up, st);
   }
   int rc = post_launch(ctx, "ffn_umma_kernel<gate/up>");
   if (rc) return rc;
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_DOWN, s);
-    k_down<<<ctx->sm_count, kUmmaThreads, S::SMEM, s>>>(up, st);
+    launch_chain(k_down, dim3(ctx->sm_count), dim3(kUmmaThreads), S::SMEM, s, up, st);
   }
   return post_launch(ctx, "ffn_umma_kernel<down>");
 }
@@ -571,10 +591,11 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   pp.ids64 = ids; pp.T = T; pp.K = c.top_k; pp.E = E;
   pp.offsets = ctx->offsets; pp.sorted_pair = ctx->sorted_pair; pp.inv = ctx->inv;
   pp.act_list = ctx->act_list; pp.n_act = ctx->n_act; pp.status = ctx->status;
-  const size_t smem = (size_t)(kPermuteWarps * E + 2 * E + 1) * sizeof(int);
+  const int pthreads = std::min(kPermuteMaxThreads, std::max(256, (T * c.top_k + 31) / 32 * 32));
+  const size_t smem = (size_t)((pthreads / 32) * E + E) * sizeof(int);
   {
     ProfScope prof(ctx, B200MOE_KERNEL_PERMUTE, st);
-    permute_kernel<<<1, kPermuteThreads, smem, st>>>(pp, tab);
+    launch_chain(permute_kernel, dim3(1), dim3(pthreads), smem, st, pp, tab);
   }
   if ((rc = post_launch(ctx, "permute_kernel"))) return rc;
 
@@ -599,7 +620,7 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
     using Tt = decltype(tag);
     ProfScope prof(ctx, B200MOE_KERNEL_COMBINE, st);
-    combine_kernel<Tt><<<T, kCombineThreads, 0, st>>>(cp, tab);
+    launch_chain(combine_kernel<Tt>, dim3(T), dim3(kCombineThreads), 0, st, cp, tab);
     return post_launch(ctx, "combine_kernel");
   });
 }

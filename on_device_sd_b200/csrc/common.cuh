@@ -117,6 +117,13 @@ __device__ __forceinline__ double warp_sum(double v) {
 // SiLU as torch evaluates it for a low-precision tensor: fp32 math, x / (1 + exp(-x)).
 __device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)); }
 
+// Programmatic dependent launch: every kernel of the chain is launched with the
+// programmatic-stream-serialization attribute, may start while its predecessor is still
+// running, and must call pdl_wait() before it touches anything the predecessor (or, through the
+// chain, any earlier kernel) produces or still reads.  pdl_trigger() lets the successor launch.
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 // Device status word bits (mirrors B200MOE_DEV_* of the public header).
 constexpr int kDevBadExpertId = 1;
 constexpr int kDevBadOffsets = 2;

@@ -60,6 +60,8 @@ __global__ void __launch_bounds__(S::THREADS, 1) ffn_gemv_kernel(FfnParams p, Sl
   const int row_bytes = Kdim * (int)sizeof(T);
   const int nseg = (row_bytes + SEG - 1) / SEG;
   const int groups = (Rdim + RW - 1) / RW;
+  pdl_wait();        // routing tables (and, for the down projection, h) come from the previous kernels
+  pdl_trigger();
   const int total_units = (*p.n_act) * groups;
   const int gw = blockIdx.x * S::WARPS + warp;
   const int W = gridDim.x * S::WARPS;
@@ -249,25 +251,37 @@ constexpr int kCombineThreads = 256;
 template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams p, SlotTable st) {
   __shared__ int s_pos[kMaxTopK];
   __shared__ float s_w[kMaxTopK];
+  __shared__ int s_rank[kMaxTopK];
+  __shared__ int s_order[kMaxTopK];
   __shared__ int s_n;
   const int t = blockIdx.x;
+  pdl_wait();        // y comes from the down projection launched just before
+  pdl_trigger();
+  // slot k of the token is read by thread k; thread 0 then orders the live ones by rank
+  if (threadIdx.x < p.K) {
+    const int k = threadIdx.x;
+    const long long e = p.ids64[(size_t)t * p.K + k];
+    int pos = -1, r = 0;
+    float w = 0.0f;
+    if (e >= 0 && e < p.E && st.slot[e] >= 0) {
+      pos = p.inv[(size_t)t * p.K + k];
+      w = p.scores_f32 ? reinterpret_cast<const float*>(p.scores)[(size_t)t * p.K + k]
+                       : Elem<T>::to_float(reinterpret_cast<const T*>(p.scores)[(size_t)t * p.K + k]);
+      r = st.rank[e];
+    }
+    s_pos[k] = pos; s_w[k] = w; s_rank[k] = r;
+  }
+  __syncthreads();
   if (threadIdx.x == 0) {
-    int rk[kMaxTopK];
     int n = 0;
     for (int k = 0; k < p.K; ++k) {
-      const long long e = p.ids64[(size_t)t * p.K + k];
-      if (e < 0 || e >= p.E || st.slot[e] < 0) continue;
-      const int pos = p.inv[(size_t)t * p.K + k];
-      if (pos < 0) continue;
-      const float w = p.scores_f32 ? reinterpret_cast<const float*>(p.scores)[(size_t)t * p.K + k]
-                                   : Elem<T>::to_float(reinterpret_cast<const T*>(p.scores)[(size_t)t * p.K + k]);
-      const int r = st.rank[e];
+      if (s_pos[k] < 0) continue;
       int i = n++;
-      while (i > 0 && rk[i - 1] > r) {  // stable insertion: equal ranks keep slot order
-        rk[i] = rk[i - 1]; s_pos[i] = s_pos[i - 1]; s_w[i] = s_w[i - 1];
+      while (i > 0 && s_rank[s_order[i - 1]] > s_rank[k]) {  // stable insertion: equal ranks keep slot order
+        s_order[i] = s_order[i - 1];
         --i;
       }
-      rk[i] = r; s_pos[i] = pos; s_w[i] = w;
+      s_order[i] = k;
     }
     s_n = n;
   }
@@ -278,17 +292,29 @@ template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine
     float acc[8];
 #pragma unroll
     for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-    for (int j = 0; j < n; ++j) {
-      Chunk<T> yc;
-      yc.template load<false>(y + (size_t)s_pos[j] * p.H + c * 8);
-      float yf[8];
-      yc.unpack(yf);
-      const float w = s_w[j];
+    for (int j0 = 0; j0 < n; j0 += 4) {
+      Chunk<T> yc[4];
+      float w[4];
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        // __fmul_rn / __fadd_rn are never contracted into an FMA: the reference multiplies, then adds
-        const float prod = p.scores_f32 ? __fmul_rn(yf[i], w) : rn<T>(__fmul_rn(yf[i], w));
-        acc[i] = rn<T>(__fadd_rn(acc[i], prod));
+      for (int u = 0; u < 4; ++u) {
+        if (j0 + u < n) {
+          const int k = s_order[j0 + u];
+          yc[u].template load<false>(y + (size_t)s_pos[k] * p.H + c * 8);
+          w[u] = s_w[k];
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < 4; ++u) {
+        if (j0 + u < n) {
+          float yf[8];
+          yc[u].unpack(yf);
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            // __fmul_rn / __fadd_rn are never contracted into an FMA: the reference multiplies, then adds
+            const float prod = p.scores_f32 ? __fmul_rn(yf[i], w[u]) : rn<T>(__fmul_rn(yf[i], w[u]));
+            acc[i] = rn<T>(__fadd_rn(acc[i], prod));
+          }
+        }
       }
     }
     if (p.residual != nullptr) {

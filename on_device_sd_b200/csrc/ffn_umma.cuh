@@ -142,6 +142,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   const int Rdim = DUAL ? p.I : p.H;
   const int nkb = (Kdim + kUmmaBK - 1) / kUmmaBK;
   const int tiles = (Rdim + TILE_ROWS - 1) / TILE_ROWS;
+
+  // Gate/up follows the permute kernel directly and needs its tables at once.  The down
+  // projection follows gate/up: the tables were complete before gate/up could start, so its
+  // weight stream starts immediately and only the loaders (readers of h) wait for gate/up to finish.
+  if (DUAL) pdl_wait();
+  pdl_trigger();
   const int total = (*p.n_act) * tiles;
 
   if (threadIdx.x == 0) {
@@ -228,6 +234,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   } else if (warp < 6) {
     // ------------------------------ token-tile loaders ------------------------------
     const int tl = threadIdx.x - 64;          // 0..127
+    if (!DUAL) pdl_wait();                    // h must be complete
     int s = 0, lag_s = 0, issued = 0;         // stage being filled; oldest stage not yet signalled
     uint32_t ph = 0;
     bool ok = true;

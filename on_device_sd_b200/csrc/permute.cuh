@@ -27,21 +27,53 @@ struct PermuteParams {
   int* status;
 };
 
-constexpr int kPermuteThreads = 1024;
-constexpr int kPermuteWarps = kPermuteThreads / 32;
+constexpr int kPermuteMaxThreads = 1024;
 
-__global__ void __launch_bounds__(kPermuteThreads) permute_kernel(PermuteParams p, SlotTable st) {
+// exclusive prefix sum over the first 256 threads of the block (E <= 256); `warp_tot` has 8 slots
+__device__ __forceinline__ int block_exclusive_scan_256(int v, int* warp_tot, int* total) {
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  int inc = v;
+#pragma unroll
+  for (int o = 1; o < 32; o <<= 1) {
+    const int t = __shfl_up_sync(0xffffffffu, inc, o);
+    if (lane >= o) inc += t;
+  }
+  if (warp < 8 && lane == 31) warp_tot[warp] = inc;
+  __syncthreads();
+  int base = 0;
+  if (warp < 8) {
+#pragma unroll
+    for (int w = 0; w < 8; ++w) {
+      const int t = warp_tot[w];
+      if (w < warp) base += t;
+    }
+  }
+  if (total != nullptr) {
+    int tt = 0;
+#pragma unroll
+    for (int w = 0; w < 8; ++w) tt += warp_tot[w];
+    *total = tt;
+  }
+  __syncthreads();
+  return base + inc - v;
+}
+
+// One CTA of 256..1024 threads (a multiple of 32, at least 256 so that every expert has a thread).
+__global__ void __launch_bounds__(kPermuteMaxThreads) permute_kernel(PermuteParams p, SlotTable st) {
   extern __shared__ int smem[];
-  int* cnt = smem;                       // [warps][E]
-  int* tot = smem + kPermuteWarps * p.E; // [E]
-  int* offs = tot + p.E;                 // [E+1]
+  const int nwarps = blockDim.x >> 5;
+  int* cnt = smem;                  // [nwarps][E]
+  int* offs = smem + nwarps * p.E;  // [E]
+  __shared__ int warp_tot[8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int E = p.E, npairs = p.T * p.K;
   // contiguous, 32-aligned slice of the pair list per warp
-  const int per_warp = ((npairs + kPermuteWarps - 1) / kPermuteWarps + 31) / 32 * 32;
+  const int per_warp = ((npairs + nwarps - 1) / nwarps + 31) / 32 * 32;
   const int begin = warp * per_warp, end = min(begin + per_warp, npairs);
 
-  for (int i = threadIdx.x; i < kPermuteWarps * E; i += kPermuteThreads) cnt[i] = 0;
+  for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) cnt[i] = 0;
+  pdl_wait();        // ids come from the router launched just before
+  pdl_trigger();
   __syncthreads();
 
   for (int b = begin; b < end; b += 32) {
@@ -54,27 +86,27 @@ __global__ void __launch_bounds__(kPermuteThreads) permute_kernel(PermuteParams 
   }
   __syncthreads();
 
+  int tot = 0;
   if (threadIdx.x < E) {
-    int run = 0;
-    for (int w = 0; w < kPermuteWarps; ++w) {
+    for (int w = 0; w < nwarps; ++w) {
       const int c = cnt[w * E + threadIdx.x];
-      cnt[w * E + threadIdx.x] = run;
-      run += c;
+      cnt[w * E + threadIdx.x] = tot;
+      tot += c;
     }
-    tot[threadIdx.x] = run;
   }
-  __syncthreads();
-  if (threadIdx.x <= E) {
-    int s = 0;
-    for (int e = 0; e < (int)threadIdx.x; ++e) s += tot[e];
-    offs[threadIdx.x] = s;
-    p.offsets[threadIdx.x] = s;
+  int grand = 0;
+  const int my_off = block_exclusive_scan_256(threadIdx.x < E ? tot : 0, warp_tot, &grand);
+  const bool active = threadIdx.x < E && tot > 0 && st.slot[threadIdx.x] >= 0;
+  int n_active = 0;
+  const int my_rank = block_exclusive_scan_256(active ? 1 : 0, warp_tot, &n_active);
+  if (threadIdx.x < E) {
+    offs[threadIdx.x] = my_off;
+    p.offsets[threadIdx.x] = my_off;
+    if (active) p.act_list[my_rank] = threadIdx.x;
   }
-  if (threadIdx.x == kPermuteThreads - 1) {
-    int n = 0;
-    for (int e = 0; e < E; ++e)
-      if (tot[e] > 0 && st.slot[e] >= 0) p.act_list[n++] = e;
-    *p.n_act = n;
+  if (threadIdx.x == 0) {
+    p.offsets[E] = grand;
+    *p.n_act = n_active;
   }
   __syncthreads();
 

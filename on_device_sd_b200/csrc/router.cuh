@@ -186,6 +186,8 @@ template <typename T, int TT, int U> __global__ void __launch_bounds__(kRouterTh
   const int nch = p.H / 8;
   const T* x = reinterpret_cast<const T*>(p.x);
   const T* bias = reinterpret_cast<const T*>(p.bias);
+  pdl_wait();        // the previous call's combine may still read the ids / scores this kernel rewrites
+  pdl_trigger();
 
   if (e < p.E) {
     const T* wrow = reinterpret_cast<const T*>(p.wg) + (size_t)e * p.H;
@@ -268,6 +270,8 @@ template <typename T> __global__ void __launch_bounds__(kRouterThreads) router_f
   __shared__ int sidx[kRouterThreads / 32][32];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t = blockIdx.x * (kRouterThreads / 32) + warp;
+  pdl_wait();
+  pdl_trigger();
   if (t < p.T) topk_softmax_token<T>(p, t, lane, skey[warp], sidx[warp]);
 }
 
