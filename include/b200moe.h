@@ -148,6 +148,25 @@ int b200moe_forward_fused(b200moe_ctx* ctx, int layer, const void* x, int T, con
 int b200moe_expert_ffn(b200moe_ctx* ctx, const void* x, int n, const void* gate_proj, const void* up_proj,
                        const void* down_proj, void* out, void* stream);
 
+/* The same FFN for callers that cannot allocate device memory.  It has no counterpart in the
+ * reference.  b200moe_expert_ffn needs a context, and creating one allocates its workspace; an
+ * engine that has already handed the whole GPU to its own pools, or code running inside a section
+ * where cudaMalloc's device-wide synchronisation is not acceptable, cannot do that.  This entry
+ * point takes no context and calls no allocator of any kind: the SwiGLU intermediate and the
+ * kernels' bookkeeping live in one fixed device array inside the library (about 2 MiB, held by
+ * every GPU that loads the library until the process exits).
+ *   x [n,H], out [n,H], gate_proj / up_proj [I,H], down_proj [H,I], all of `dtype`, on the CURRENT
+ *   device, 16-byte aligned; H and I multiples of 8.
+ *   Limits: n <= 64 and n * I * sizeof(element) <= 2 MiB; larger calls fail with
+ *   B200MOE_E_UNSUPPORTED and a message (use b200moe_expert_ffn then).
+ *   The first call on a device looks up the device address of the array; make that first call
+ *   before starting any stream capture.
+ *   All calls share the array, which keeps the last call's contents (each call clears the words
+ *   that must start at zero): calls that overlap on the GPU race - serialise them. */
+int b200moe_expert_ffn_noalloc(const void* x, int n, int hidden_size, int intermediate_size, int dtype,
+                               const void* gate_proj, const void* up_proj, const void* down_proj, void* out,
+                               void* stream);
+
 /* Int4 g128 packer / unpacker.  Not in the reference (it has no quantised weights); the format
  * is the one documented at b200moe_set_expert.  w [out,in] in `dtype`; q uint8 [out,in/2];
  * scales bf16 [out,in/128].  unpack writes q_out int8 [out,in] (values -8..7, may be NULL) and

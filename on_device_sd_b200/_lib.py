@@ -47,6 +47,7 @@ PROTOTYPES = {
                                 POINTER(c_int32), c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_forward_fused": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_expert_ffn": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200moe_expert_ffn_noalloc": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_pack_int4": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_unpack_int4": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_profile": (c_int, [c_void_p, c_int]),

@@ -16,6 +16,7 @@
 #include <vector>
 
 #include "common.cuh"
+#include "internal.h"
 #include "ffn_gemv.cuh"
 #include "int4_pack.cuh"
 #include "permute.cuh"
@@ -97,6 +98,16 @@ static int fail(b200moe_ctx* ctx, int code, const char* fmt, ...) {
   vsnprintf(buf, sizeof buf, fmt, ap);
   va_end(ap);
   if (ctx) ctx->err = buf;
+  g_err = buf;
+  return code;
+}
+
+int b200moe_fail_global(int code, const char* fmt, ...) {
+  char buf[512];
+  va_list ap;
+  va_start(ap, fmt);
+  vsnprintf(buf, sizeof buf, fmt, ap);
+  va_end(ap);
   g_err = buf;
   return code;
 }

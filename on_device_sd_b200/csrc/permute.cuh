@@ -59,7 +59,7 @@ __device__ __forceinline__ int block_exclusive_scan_256(int v, int* warp_tot, in
 }
 
 // One CTA of 256..1024 threads (a multiple of 32, at least 256 so that every expert has a thread).
-__global__ void __launch_bounds__(kPermuteMaxThreads) permute_kernel(PermuteParams p, SlotTable st) {
+static __global__ void __launch_bounds__(kPermuteMaxThreads) permute_kernel(PermuteParams p, SlotTable st) {
   extern __shared__ int smem[];
   const int nwarps = blockDim.x >> 5;
   int* cnt = smem;                  // [nwarps][E]
