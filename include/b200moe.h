@@ -143,6 +143,23 @@ int b200moe_forward(b200moe_ctx* ctx, int layer, const void* x, int T, const int
 int b200moe_forward_fused(b200moe_ctx* ctx, int layer, const void* x, int T, const void* residual, void* out,
                           int64_t* ids_out, void* scores_out, int ffn_kind, void* stream);
 
+/* Expert parallelism (no counterpart in the reference, which runs on one GPU; its future-work
+ * note is demo/others.md:58-62).  Rank r registers only the experts it owns (contiguous blocks of
+ * E/G); the router weight is replicated; each rank routes its own tokens with b200moe_route.
+ * Between the two calls below the host layer runs two fixed-size collectives over NCCL:
+ * all-gather of (x, ids) before, sum reduce-scatter of the pair-ordered outputs after.
+ *
+ * b200moe_ep_local_experts: expert FFN over ALL ranks' tokens for the experts registered here.
+ *   x_all [T_all,H], ids_all int64 [T_all,K] -> y_pairs_out [T_all*K, H] in pair order (row
+ *   t*K+k); rows of pairs whose expert lives elsewhere are written as zeros, so summing the
+ *   buffers of all ranks reassembles every pair exactly.
+ * b200moe_ep_combine: weighted accumulation for this rank's own tokens from their pair rows
+ *   y_pairs [T*K, H] (all experts present), same order / rounding rules as b200moe_forward. */
+int b200moe_ep_local_experts(b200moe_ctx* ctx, int layer, const void* x_all, int T_all, const int64_t* ids_all,
+                             void* y_pairs_out, int ffn_kind, void* stream);
+int b200moe_ep_combine(b200moe_ctx* ctx, const void* y_pairs, int T, const int64_t* ids, const void* scores, int scores_dtype,
+                       const int32_t* order, const void* residual, void* out, void* stream);
+
 /* One expert's SwiGLU FFN on n rows: expert_forward_with_weights (demo/src/layers/mlp.py:209-231).
  * Dense weights in the activation dtype; x [n,H] -> out [n,H]. */
 int b200moe_expert_ffn(b200moe_ctx* ctx, const void* x, int n, const void* gate_proj, const void* up_proj,

@@ -46,6 +46,8 @@ PROTOTYPES = {
     "b200moe_forward": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, POINTER(c_int32),
                                 POINTER(c_int32), c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_forward_fused": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "b200moe_ep_local_experts": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
+    "b200moe_ep_combine": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, POINTER(c_int32), c_void_p, c_void_p, c_void_p]),
     "b200moe_expert_ffn": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_expert_ffn_noalloc": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_pack_int4": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

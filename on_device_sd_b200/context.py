@@ -198,6 +198,31 @@ class MoEContext:
                                                     ffn_kind, _stream(self.device)))
         return (out, ids, scores) if return_routing else out
 
+    def ep_local_experts(self, layer: int, x_all: torch.Tensor, ids_all: torch.Tensor, *, ffn_kind: int = FFN_AUTO,
+                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Expert-parallel leg 1: FFN of the experts registered here over all ranks' tokens -> [T_all*K, H] in pair order."""
+        _need_cuda(x_all, "x_all", self.device, self.dtype)
+        _need_cuda(ids_all, "ids_all", self.device, torch.int64)
+        T = x_all.shape[0]
+        if out is None:
+            out = torch.empty(T * self.K, self.H, dtype=self.dtype, device=self.device)
+        self._check(self._lib.b200moe_ep_local_experts(self._h, layer, _ptr(x_all), T, _ptr(ids_all), _ptr(out), ffn_kind, _stream(self.device)))
+        return out
+
+    def ep_combine(self, y_pairs: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, *, order: Optional[Sequence[int]] = None,
+                   residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        """Expert-parallel leg 2: weighted accumulation of this rank's tokens from their pair rows [T*K, H]."""
+        _need_cuda(y_pairs, "y_pairs", self.device, self.dtype)
+        _need_cuda(ids, "ids", self.device, torch.int64)
+        T = ids.shape[0]
+        scores = scores.contiguous()
+        if out is None:
+            out = torch.empty(T, self.H, dtype=self.dtype, device=self.device)
+        order_arr = (c_int32 * self.E)(*order) if order is not None else None
+        self._check(self._lib.b200moe_ep_combine(self._h, _ptr(y_pairs), T, _ptr(ids), _ptr(scores), dtype_tag(scores.dtype), order_arr,
+                                                 _ptr(residual), _ptr(out), _stream(self.device)))
+        return out
+
     def expert_ffn(self, x2d: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor, down_proj: torch.Tensor) -> torch.Tensor:
         for name, t in (("x", x2d), ("gate_proj", gate_proj), ("up_proj", up_proj), ("down_proj", down_proj)):
             _need_cuda(t, name, self.device, self.dtype)

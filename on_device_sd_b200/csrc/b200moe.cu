@@ -215,7 +215,7 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
   ctx->y = yb;
   ctx->scores = sb;
 #ifdef B200MOE_WITH_UMMA
-  if (cfg->act_dtype == B200MOE_BF16 && cfg->weight_mode == B200MOE_W_DENSE) {
+  if (cfg->act_dtype == B200MOE_BF16) {   // dense bf16 (tcgen05 path) and int4 (TMA boxes of packed nibbles)
     ctx->h_tmaps.assign((L * E + 1) * 3, CUtensorMap{});
     ctx->tmap_ok.assign(L * E + 1, 0);
     if ((rc = dev_alloc(ctx, &ctx->d_tmaps, (L * E + 1) * 3))) {
@@ -304,7 +304,24 @@ static bool encode_map(b200moe_ctx* ctx, CUtensorMap* out, const void* base, int
   return r == CUDA_SUCCESS;
 }
 
+// packed int4 matrix, uint8 [rows, bytes_per_row] -> 2-D map with a {128 bytes, 16 rows} box, 128-byte swizzle
+static bool encode_map_u8(b200moe_ctx* ctx, CUtensorMap* out, const void* base, int rows, int bytes_per_row) {
+  if (!ctx->encode_fn) return false;
+  const cuuint64_t dims[2] = {(cuuint64_t)bytes_per_row, (cuuint64_t)rows};
+  const cuuint64_t strides[1] = {(cuuint64_t)bytes_per_row};
+  const cuuint32_t box[2] = {128u, 16u};
+  const cuuint32_t estr[2] = {1u, 1u};
+  CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_fn)(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
+                                                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                               CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS;
+}
+
 static bool encode_expert_maps(b200moe_ctx* ctx, CUtensorMap* three, const void* gate, const void* up, const void* down) {
+  const int H0 = ctx->cfg.hidden_size, I0 = ctx->cfg.intermediate_size;
+  if (ctx->cfg.weight_mode == B200MOE_W_INT4_G128)
+    return encode_map_u8(ctx, &three[0], gate, I0, H0 / 2) && encode_map_u8(ctx, &three[1], up, I0, H0 / 2) &&
+           encode_map_u8(ctx, &three[2], down, H0, I0 / 2);
   const int H = ctx->cfg.hidden_size, I = ctx->cfg.intermediate_size;
   return encode_map(ctx, &three[0], gate, I, H, 64) && encode_map(ctx, &three[1], up, I, H, 64) &&
          encode_map(ctx, &three[2], down, H, I, 128);
@@ -548,6 +565,41 @@ static int launch_ffn_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tma
 }
 #endif
 
+#ifdef B200MOE_WITH_INT4
+template <int NTILE> static int launch_int4_pair(b200moe_ctx* ctx, const Int4Params& ip, const SlotTable& st, cudaStream_t s) {
+  auto k_up = ffn_int4_kernel<true, NTILE>;
+  auto k_down = ffn_int4_kernel<false, NTILE>;
+  static bool configured = false;
+  if (!configured) {
+    CUDA_TRY(ctx, cudaFuncSetAttribute(k_up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kInt4Smem));
+    CUDA_TRY(ctx, cudaFuncSetAttribute(k_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kInt4Smem));
+    configured = true;
+  }
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
+    launch_chain(k_up, dim3(ctx->sm_count), dim3(kInt4Threads), kInt4Smem, s, ip, st);
+  }
+  int rc = post_launch(ctx, "ffn_int4_kernel<gate/up>");
+  if (rc) return rc;
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_FFN_DOWN, s);
+    launch_chain(k_down, dim3(ctx->sm_count), dim3(kInt4Threads), kInt4Smem, s, ip, st);
+  }
+  return post_launch(ctx, "ffn_int4_kernel<down>");
+}
+
+static int launch_ffn_int4(b200moe_ctx* ctx, const FfnParams& p, const void* tmaps, const SlotTable& st, int max_n, cudaStream_t s) {
+  if (!tmaps) return fail(ctx, B200MOE_E_STATE, "int4 path: no TMA descriptors for these experts (cuTensorMapEncodeTiled unavailable or failed)");
+  Int4Params ip{};
+  ip.f = p;
+  ip.tmaps = reinterpret_cast<const CUtensorMap*>(tmaps);
+  ip.status = ctx->status;
+  if (max_n <= 8) return launch_int4_pair<1>(ctx, ip, st, s);
+  if (max_n <= 16) return launch_int4_pair<2>(ctx, ip, st, s);
+  return launch_int4_pair<4>(ctx, ip, st, s);
+}
+#endif
+
 static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st, int ffn_kind, cudaStream_t s) {
   const b200moe_config& c = ctx->cfg;
   FfnParams p{};
@@ -556,7 +608,7 @@ static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st,
   p.H = c.hidden_size; p.I = c.intermediate_size; p.K = f.K;
   if (c.weight_mode == B200MOE_W_INT4_G128) {
 #ifdef B200MOE_WITH_INT4
-    return launch_ffn_int4(ctx->sm_count, p, st, f.max_n, s, [&](const char* what) { return post_launch(ctx, what); });
+    return launch_ffn_int4(ctx, p, f.tmaps, st, f.max_n, s);
 #else
     return fail(ctx, B200MOE_E_UNSUPPORTED, "library built without the int4 kernels");
 #endif
@@ -624,6 +676,20 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
 #endif
   if ((rc = launch_ffn(ctx, f, tab, ffn_kind, st))) return rc;
 
+  if (scores == nullptr) {
+    // expert-parallel leg: no combine here; the expert outputs go back to pair order (t*K + k),
+    // zero rows for pairs served by other ranks, ready for a sum reduce-scatter
+    ScatterParams sp{};
+    sp.y = ctx->y; sp.inv = ctx->inv; sp.ids64 = ids; sp.out = out;
+    sp.npairs = T * c.top_k; sp.H = c.hidden_size; sp.E = E;
+    return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
+      using Tt = decltype(tag);
+      ProfScope prof(ctx, B200MOE_KERNEL_COMBINE, st);
+      launch_chain(scatter_pairs_kernel<Tt>, dim3(sp.npairs), dim3(kCombineThreads), 0, st, sp, tab);
+      return post_launch(ctx, "scatter_pairs_kernel");
+    });
+  }
+
   CombineParams cp{};
   cp.y = ctx->y; cp.inv = ctx->inv; cp.ids64 = ids; cp.scores = scores;
   cp.scores_f32 = (scores_dtype == B200MOE_F32 && c.act_dtype != B200MOE_F32) ? 1 : 0;
@@ -671,6 +737,58 @@ extern "C" int b200moe_forward_fused(b200moe_ctx* ctx, int layer, const void* x,
   void* scores = scores_out ? scores_out : ctx->scores;
   if ((rc = launch_router(ctx, layer, x, nullptr, T, ids, scores, nullptr, st))) return rc;
   return run_experts(ctx, layer, x, T, ids, scores, ctx->cfg.act_dtype, nullptr, nullptr, residual, out, ffn_kind, st);
+}
+
+// ------------------------------------------------------------------------------------------
+// expert-parallel legs
+// ------------------------------------------------------------------------------------------
+extern "C" int b200moe_ep_local_experts(b200moe_ctx* ctx, int layer, const void* x_all, int T_all, const int64_t* ids_all,
+                                        void* y_pairs_out, int ffn_kind, void* stream) {
+  int rc = check_layer(ctx, layer, "b200moe_ep_local_experts");
+  if (rc) return rc;
+  if ((rc = check_tokens(ctx, T_all, "b200moe_ep_local_experts"))) return rc;
+  if (T_all == 0) return B200MOE_OK;
+  if (!x_all || !ids_all || !y_pairs_out) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_local_experts: null pointer");
+  if (misaligned(x_all) || misaligned(y_pairs_out)) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_local_experts: x_all and y_pairs_out must be 16-byte aligned");
+  if (ffn_kind < B200MOE_FFN_AUTO || ffn_kind > B200MOE_FFN_MMA) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_local_experts: unknown ffn_kind %d", ffn_kind);
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  // scores == nullptr selects the scatter-to-pair-order ending of run_experts; experts that are not
+  // registered on this rank are skipped, which is exactly the sharding
+  return run_experts(ctx, layer, x_all, T_all, ids_all, nullptr, ctx->cfg.act_dtype, nullptr, nullptr, nullptr, y_pairs_out, ffn_kind,
+                     reinterpret_cast<cudaStream_t>(stream));
+}
+
+extern "C" int b200moe_ep_combine(b200moe_ctx* ctx, const void* y_pairs, int T, const int64_t* ids, const void* scores, int scores_dtype,
+                                  const int32_t* order, const void* residual, void* out, void* stream) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_ep_combine: null context");
+  int rc = check_tokens(ctx, T, "b200moe_ep_combine");
+  if (rc) return rc;
+  if (T == 0) return B200MOE_OK;
+  if (!y_pairs || !ids || !scores || !out) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_combine: null pointer");
+  if (misaligned(y_pairs) || misaligned(out) || (residual && misaligned(residual)))
+    return fail(ctx, B200MOE_E_ARG, "b200moe_ep_combine: y_pairs, out and residual must be 16-byte aligned");
+  const b200moe_config& c = ctx->cfg;
+  if (scores_dtype != c.act_dtype && scores_dtype != B200MOE_F32) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_combine: scores must be in the activation dtype or fp32");
+  CUDA_TRY(ctx, cudaSetDevice(c.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  SlotTable tab;
+  for (int e = 0; e < kMaxExperts; ++e) { tab.slot[e] = (int16_t)(e < c.num_experts ? e : -1); tab.rank[e] = (uint8_t)(e & 255); }
+  if (order)
+    for (int e = 0; e < c.num_experts; ++e) {
+      if (order[e] < 0 || order[e] > 255) return fail(ctx, B200MOE_E_ARG, "order[%d]=%d out of range [0,255]", e, order[e]);
+      tab.rank[e] = (uint8_t)order[e];
+    }
+  CombineParams cp{};
+  cp.y = y_pairs; cp.inv = ctx->one_sorted;   // identity: pair p lives in row p
+  cp.ids64 = ids; cp.scores = scores;
+  cp.scores_f32 = (scores_dtype == B200MOE_F32 && c.act_dtype != B200MOE_F32) ? 1 : 0;
+  cp.residual = residual; cp.out = out; cp.T = T; cp.H = c.hidden_size; cp.K = c.top_k; cp.E = c.num_experts;
+  return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
+    using Tt = decltype(tag);
+    ProfScope prof(ctx, B200MOE_KERNEL_COMBINE, st);
+    launch_chain(combine_kernel<Tt>, dim3(T), dim3(kCombineThreads), 0, st, cp, tab);
+    return post_launch(ctx, "combine_kernel");
+  });
 }
 
 extern "C" int b200moe_expert_ffn(b200moe_ctx* ctx, const void* x, int n, const void* gate_proj, const void* up_proj,

@@ -330,3 +330,36 @@ template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine
 }
 
 }  // namespace b200moe
+
+namespace b200moe {
+
+// Expert-parallel return leg: expert outputs from sorted-pair order back to pair order
+// (row t*K + k), zeros for pairs whose expert this rank does not serve.  Every row of `out` is
+// written, so the buffer needs no clearing and a sum over ranks reassembles all pairs exactly
+// (each row is non-zero on one rank only).
+struct ScatterParams {
+  const void* y;         // [pairs, H] sorted-pair order
+  const int* inv;        // [npairs]
+  const int64_t* ids64;  // [npairs]
+  void* out;             // [npairs, H]
+  int npairs, H, E;
+};
+
+template <typename T> __global__ void __launch_bounds__(kCombineThreads) scatter_pairs_kernel(ScatterParams p, SlotTable st) {
+  const int pr = blockIdx.x;
+  pdl_wait();
+  pdl_trigger();
+  const long long e = p.ids64[pr];
+  const int pos = (e >= 0 && e < p.E && st.slot[e] >= 0) ? p.inv[pr] : -1;
+  const T* y = reinterpret_cast<const T*>(p.y);
+  for (int c = threadIdx.x; c < p.H / 8; c += kCombineThreads) {
+    Chunk<T> v;
+    if (pos >= 0) v.template load<false>(y + (size_t)pos * p.H + c * 8);
+    else v.zero();
+    float f[8];
+    v.unpack(f);
+    store_chunk<T>(reinterpret_cast<T*>(p.out) + (size_t)pr * p.H + c * 8, f);
+  }
+}
+
+}  // namespace b200moe

@@ -35,8 +35,16 @@ def _close(got, want, dtype, tight=False):
     if tight and dtype != torch.float32:
         tol_r = 1e-3     # same rounding points and same accumulation order: far inside the budget
     ulp = {torch.float32: 0.0, torch.float16: 2.0 ** -9, torch.bfloat16: 2.0 ** -6}[dtype]
-    excess = float(((got - want).abs() - (tol_a + ulp * want.abs())).max()) if got.numel() else -1.0
-    assert excess <= 0 and mr <= tol_r, (ma, mr, excess)
+    if not got.numel():
+        return ma, mr
+    # A token's output is a model-dtype sum of expert outputs that can cancel: the unit in the last
+    # place that matters is that of the largest term, not of the (possibly tiny) result.  So every
+    # element must lie within two ulps of the tensor's largest magnitude, and all but one in ten
+    # thousand within two ulps of their own magnitude.
+    diff = (got - want).abs()
+    excess = float((diff - (tol_a + ulp * want.abs().max())).max())
+    outliers = float((diff > tol_a + ulp * want.abs()).double().mean())
+    assert excess <= 0 and outliers <= 1e-4 and mr <= tol_r, (ma, mr, excess, outliers)
     return ma, mr
 
 
