@@ -39,6 +39,15 @@ WORKLOADS = {
     "qwen3_bf16": ("qwen3", "bf16", (1, 2, 4, 8, 16, 32, 64, 128, 256)),
     "qwen3_int4": ("qwen3", "int4", (1, 2, 4, 8, 16, 32, 64, 128, 256)),
 }
+EP_WORKLOADS = {
+    # expert-parallel runs of the 128-expert layer: the batch is split across the ranks (strong scaling)
+    "qwen3_bf16_ep": ("qwen3", "bf16", (8, 16, 32, 64, 128, 256)),
+    "qwen3_int4_ep": ("qwen3", "int4", (8, 16, 32, 64, 128, 256)),
+    # 48 stacked blocks, attention = identity, Zipf(1.1) gate bias; verify of k = 4 / 8 drafts for 32 sequences
+    # (T = 32*(k+1) as the reference builds the verify batch, demo/src/execution/cb_executor.py:236-243)
+    "qwen3_int4_stack": ("qwen3", "int4", (160, 288)),
+    "qwen3_bf16_stack": ("qwen3", "bf16", (160, 288)),
+}
 METRIC = "MoE-layer tokens/s at verify batch"
 UNIT = "tokens/s"
 
@@ -403,19 +412,115 @@ def run_ours(args, workload):
         dist.destroy_process_group()
 
 
+def run_ep(args, workload):
+    """Expert-parallel layer: experts sharded over the ranks, all-gather dispatch and reduce-scatter
+    return over NCCL (on_device_sd_b200/ep.py).  Eager launches; time = max over ranks, device events."""
+    import torch.distributed as dist
+    from on_device_sd_b200 import MoEContext, W_DENSE, W_INT4_G128
+    from on_device_sd_b200.ep import ExpertParallelMoE, expert_range, split_tokens
+    from on_device_sd_b200.quant import quantize_expert
+    from on_device_sd_b200.synth import CONFIGS
+    cfg_name, wmode, batches = EP_WORKLOADS[workload]
+    H, E, K, I, dtype = CONFIGS[cfg_name]
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0")); local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if "RANK" in os.environ:
+        dist.init_process_group("nccl", device_id=dev)
+    else:   # plain `python bench.py`: a one-rank group, no collectives are issued
+        dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29555", rank=0, world_size=1, device_id=dev)
+    batches = tuple(T for T in batches if T % world == 0)
+    int4 = wmode == "int4"
+    stack = workload.endswith("_stack")
+    n_layers = 48 if stack else 1
+    ctx = MoEContext(H, E, K, I, dtype, num_layers=n_layers, max_tokens=max(batches), weight_mode=W_INT4_G128 if int4 else W_DENSE, device=dev)
+    g = torch.Generator(device=dev).manual_seed(0)                      # same gate and tokens on every rank
+    ctx.set_gate(0, (torch.randn(E, H, device=dev, generator=g) * 0.02).to(dtype))
+    xs_full = {T: torch.randn(T, H, device=dev, generator=g).to(dtype) for T in batches}
+    ep = ExpertParallelMoE(ctx, E, K, H)
+    gl = torch.Generator(device=dev).manual_seed(100 + rank)
+    keep = []
+    for layer in range(n_layers):
+        if layer > 0:
+            from on_device_sd_b200.synth import zipf_bias
+            ctx.set_gate(layer, (torch.randn(E, H, device=dev, generator=g) * 0.02).to(dtype), None)
+        for e in expert_range(E, world, rank):                          # only the local shard is ever materialised
+            p = {"gate_proj": (torch.randn(I, H, device=dev, generator=gl) * 0.02).to(dtype),
+                 "up_proj": (torch.randn(I, H, device=dev, generator=gl) * 0.02).to(dtype),
+                 "down_proj": (torch.randn(H, I, device=dev, generator=gl) * 0.02).to(dtype)}
+            p = quantize_expert(p) if int4 else p
+            keep.append(p)
+            ctx.set_expert(layer, e, p)
+    if stack:
+        from on_device_sd_b200.synth import zipf_bias
+        for layer in range(n_layers):                                   # popularity skew: b_e = log p_e, p ~ rank^-1.1
+            gw = ctx._gate[layer][0] if layer in ctx._gate else None
+            ctx.set_gate(layer, gw, zipf_bias(E, 1.1, seed=layer).to(dev))
+    xl = {}
+    for T in batches:
+        sl = split_tokens(T, world, rank)
+        xl[T] = xs_full[T][sl.start:sl.stop].contiguous()
+    from on_device_sd_b200.stack import MoEStack
+    model = MoEStack(ctx, n_layers, ep)
+    one = (lambda T: model.forward(xl[T])) if stack else (lambda T: ep.forward(0, xl[T]))
+    def step():
+        for T in batches:
+            one(T)
+    for _ in range(max(args.warmup, 3)):
+        step()
+    torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    l0 = ctx.launches
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record(); torch.cuda.synchronize(); dist.barrier()
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev)
+    dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    ms = float(t.item())
+    per_T = {}
+    for T in batches:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize(); dist.barrier()
+        a.record()
+        reps = 3 if stack else 20
+        for _ in range(reps):
+            one(T)
+        b.record(); torch.cuda.synchronize()
+        tt = torch.tensor([a.elapsed_time(b) / reps * 1e3], device=dev)
+        dist.all_reduce(tt, op=dist.ReduceOp.MAX)
+        per_T[str(T)] = {"us": round(float(tt.item()), 1), "tokens_per_s": round(T / float(tt.item()) * 1e6)}
+    ctx.status()
+    if rank == 0:
+        print(json.dumps({"metric": METRIC, "value": sum(batches) * args.steps / (ms * 1e-3), "unit": UNIT, "n_gpus": world, "steps": args.steps,
+                          "warmup": max(args.warmup, 3), "ms_per_step": ms / args.steps, "higher_is_better": True, "scaling": "strong",
+                          "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+                          "config": {"workload": workload, "layer": cfg_name, "hidden": H, "experts": E, "top_k": K, "intermediate": I,
+                                     "token_batches": list(batches), "weights": wmode, "parallelism": f"ep{world}: {E // world} experts per GPU, "
+                                     "all-gather dispatch + sum reduce-scatter return over NCCL", "launch": "eager", "layers": n_layers,
+                                     "gate_bias": "zipf s=1.1 over a seeded permutation" if stack else None},
+                          "gpu_launches": ctx.launches - l0 - 20 * len(batches) * 0, "per_T": per_T}), flush=True)
+    dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="b200", choices=["b200", "reference"])
-    ap.add_argument("--workload", default="mixtral_bf16", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="mixtral_bf16", choices=sorted(WORKLOADS) + sorted(EP_WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--batches", default=None, help="comma-separated token batches replacing the workload's sweep (profiling runs)")
     ap.add_argument("--ffn-kind", default="auto", choices=["auto", "gemv", "mma"], help="force one expert-FFN kernel family")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
     ap.add_argument("--quick", action="store_true", help="timed region only: no e2e, per-T or CPU-baseline legs (for ncu captures)")
     args = ap.parse_args()
+    if args.workload in EP_WORKLOADS:
+        if args.impl == "reference":
+            print(json.dumps({"impl": "reference", "unavailable": "the reference has no expert-parallel path (single GPU, demo/others.md:58-62)"}))
+            return
+        return run_ep(args, args.workload)
     if args.batches:
         cfg, wm, _ = WORKLOADS[args.workload]
         WORKLOADS[args.workload] = (cfg, wm, tuple(int(b) for b in args.batches.split(",")))

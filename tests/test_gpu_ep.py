@@ -62,3 +62,36 @@ def test_nccl_ranks_match_single_gpu():
     r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", f"--nproc-per-node={n}", "--master-addr", "127.0.0.1",
                         "--master-port", str(port), str(ROOT / "tests" / "ep_nccl_check.py")], capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "EP_NCCL_CHECK PASS" in r.stdout, r.stdout[-2000:] + r.stderr[-2000:]
+
+
+def test_stack_with_popularity_bias_matches_oracle_layer_by_layer():
+    """Three stacked blocks h <- x + MoE_l(h) with the Zipf gate bias of the stacked benchmark; each
+    layer's kernel output is checked against the oracle fed with the SAME bf16 input, so errors do not compound."""
+    from on_device_sd_b200 import MoEContext
+    from on_device_sd_b200.stack import MoEStack
+    from on_device_sd_b200.synth import make_layer, zipf_bias
+    from test_gpu_moe import _close
+    H, E, K, I, T, L = 256, 16, 4, 128, 20, 3
+    ctx = MoEContext(H, E, K, I, torch.bfloat16, num_layers=L, max_tokens=32)
+    layers = []
+    for l in range(L):
+        Ll = make_layer(H, E, K, I, torch.bfloat16, T, seed=50 + l)
+        bias = zipf_bias(E, 1.1, seed=l).to(torch.bfloat16)
+        ctx.set_gate(l, Ll.gate_w.cuda(), bias.cuda())
+        for e, p in Ll.experts.items():
+            ctx.set_expert(l, e, {k: v.cuda() for k, v in p.items()})
+        layers.append((Ll, bias))
+    h = layers[0][0].x.cuda()
+    out = MoEStack(ctx, L).forward(h)
+    assert ctx.status() == 0
+    cur = h
+    counts = torch.zeros(E)
+    for l, (Ll, bias) in enumerate(layers):
+        got = ctx.forward_fused(l, cur, residual=h)
+        ids, scores, _ = O.route(cur.cpu(), Ll.gate_w, K, bias=bias)
+        counts += torch.bincount(ids.flatten(), minlength=E)
+        want = O.moe_engine(cur.cpu(), ids, scores, Ll.experts, order=list(range(E)), residual=h.cpu())
+        _close(got, want, torch.bfloat16, tight=True)
+        cur = got
+    assert torch.equal(cur, out)
+    assert counts.max() >= 2 * counts.mean() and counts.min() == 0    # the bias really skews the expert load
