@@ -61,6 +61,9 @@ struct b200moe_ctx {
   int* n_act = nullptr;
   void* h = nullptr;
   void* y = nullptr;
+  float* ypart = nullptr;           // fp32 K-slices of the down projection (tensor-core path)
+  int ypart_slices = 0;             // slices ypart has room for
+  int last_ksplit = 1;              // K split used by the most recent tensor-core launch
   int* status = nullptr;
   unsigned long long* bitmap = nullptr;
   // second, tiny table set used by b200moe_expert_ffn (one expert, identity permutation)
@@ -222,6 +225,11 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
       std::string msg = ctx->err;
       b200moe_destroy(ctx);
       return fail(nullptr, rc, "%s", msg.c_str());
+    }
+    if (cfg->weight_mode == B200MOE_W_DENSE) {
+      const size_t slice = pairs * (size_t)H * sizeof(float);
+      int slices = (int)std::min<size_t>(8, (64u << 20) / std::max<size_t>(slice, 1));
+      if (slices >= 2 && dev_alloc(ctx, &ctx->ypart, (size_t)slices * pairs * H) == B200MOE_OK) ctx->ypart_slices = slices;
     }
     cudaDriverEntryPointQueryResult qres;
     if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ctx->encode_fn, cudaEnableDefault, &qres) != cudaSuccess ||
@@ -489,6 +497,8 @@ struct FfnLaunch {
   int K;        // pairs per token in sorted_pair
   const void* tmaps;  // tensor maps matching `experts` (null when the tensor-core path cannot run)
   int max_n;    // upper bound on tokens per expert
+  int n_act_bound = 1;   // upper bound on the number of experts with work
+  bool ksplit_ok = false;   // the consumer of y accepts fp32 K-slices (the combine kernel does)
 };
 
 using GemvDefault = GemvShape<8, 2048, 3>;
@@ -552,12 +562,25 @@ template <int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, const UmmaPara
 
 // max_n bounds the tokens any expert can hold in this call (the batch size); a pass of the
 // kernel covers NMAX tokens, so larger per-expert counts only cost extra passes.
-static int launch_ffn_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tmaps, const SlotTable& st, int max_n, cudaStream_t s) {
+static int launch_ffn_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tmaps, const SlotTable& st, int max_n, int n_act_bound,
+                           bool ksplit_ok, cudaStream_t s) {
   if (!tmaps) return fail(ctx, B200MOE_E_UNSUPPORTED, "tensor-core path unavailable: no TMA descriptors for these experts");
   UmmaParams up{};
   up.f = p;
   up.tmaps = reinterpret_cast<const CUtensorMap*>(tmaps);
   up.status = ctx->status;
+  // K split of the down projection: aim at >= 8 work items per SM (n_act_bound experts x H/128 tiles)
+  up.ksplit = 1;
+  up.ypart = ctx->ypart;
+  up.pairs_cap = ctx->cfg.max_tokens * ctx->cfg.top_k;
+  if (ksplit_ok && ctx->ypart_slices >= 2) {
+    const int tiles = (p.H + 127) / 128, nkb = (p.I + 63) / 64;
+    const int items = std::max(1, n_act_bound * tiles);
+    int ks = (8 * ctx->sm_count + items - 1) / items;
+    ks = std::min(std::min(ks, ctx->ypart_slices), std::max(1, nkb / 16));   // a slice keeps >= 16 k-blocks (1024 of K)
+    up.ksplit = std::max(1, ks);
+  }
+  ctx->last_ksplit = up.ksplit;
   if (max_n <= 16) return launch_umma_pair<16>(ctx, up, st, s);
   if (max_n <= 32) return launch_umma_pair<32>(ctx, up, st, s);
   if (max_n <= 64) return launch_umma_pair<64>(ctx, up, st, s);
@@ -615,7 +638,7 @@ static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st,
   }
 #ifdef B200MOE_WITH_UMMA
   if (c.act_dtype == B200MOE_BF16 && ffn_kind != B200MOE_FFN_GEMV && (ffn_kind == B200MOE_FFN_MMA || f.max_n > 1)) {
-    int rc = launch_ffn_umma(ctx, p, f.tmaps, st, f.max_n, s);
+    int rc = launch_ffn_umma(ctx, p, f.tmaps, st, f.max_n, f.n_act_bound, f.ksplit_ok, s);
     if (rc != B200MOE_E_UNSUPPORTED) return rc;
     if (ffn_kind == B200MOE_FFN_MMA) return rc;
   }
@@ -666,6 +689,9 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   f.experts = ctx->d_experts + (size_t)layer * E;
   f.offsets = ctx->offsets; f.sorted_pair = ctx->sorted_pair; f.act_list = ctx->act_list; f.n_act = ctx->n_act;
   f.x = x; f.h = ctx->h; f.y = ctx->y; f.K = c.top_k; f.max_n = T;
+  f.n_act_bound = (int)std::min<long long>(E, (long long)T * c.top_k);
+  f.ksplit_ok = scores != nullptr;   // the expert-parallel scatter reads bf16 y
+  ctx->last_ksplit = 1;
 #ifdef B200MOE_WITH_UMMA
   if (!ctx->h_tmaps.empty()) {
     bool all_ok = true;
@@ -691,6 +717,7 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   }
 
   CombineParams cp{};
+  if (ctx->last_ksplit > 1) { cp.ypart = ctx->ypart; cp.y_parts = ctx->last_ksplit; cp.pairs_cap = c.max_tokens * c.top_k; }
   cp.y = ctx->y; cp.inv = ctx->inv; cp.ids64 = ids; cp.scores = scores;
   cp.scores_f32 = (scores_dtype == B200MOE_F32 && c.act_dtype != B200MOE_F32) ? 1 : 0;
   cp.residual = residual; cp.out = out; cp.T = T; cp.H = c.hidden_size; cp.K = c.top_k; cp.E = E;

@@ -57,14 +57,21 @@ __global__ void __launch_bounds__(S::THREADS, 1) ffn_gemv_kernel(FfnParams p, Sl
 
   const int Kdim = DUAL ? p.H : p.I;
   const int Rdim = DUAL ? p.I : p.H;
-  const int row_bytes = Kdim * (int)sizeof(T);
-  const int nseg = (row_bytes + SEG - 1) / SEG;
-  const int groups = (Rdim + RW - 1) / RW;
   pdl_wait();        // routing tables (and, for the down projection, h) come from the previous kernels
   pdl_trigger();
-  const int total_units = (*p.n_act) * groups;
   const int gw = blockIdx.x * S::WARPS + warp;
   const int W = gridDim.x * S::WARPS;
+  // When the down projection has too few four-row units to keep every warp of the grid busy
+  // (single-token batches: 2 experts x 1024 units on 1184 warps), a unit becomes ONE row whose
+  // four streams are the four quarters of K; the partial sums are added before the reduction.
+  // Only for rows long enough that a quarter still fills a whole ring segment.
+  const bool ksplit = !DUAL && (Kdim % 32 == 0) && Kdim * (int)sizeof(T) >= 4 * SEG && ((*p.n_act) * ((Rdim + RW - 1) / RW) < 6 * W);
+  const int rows_per_unit = ksplit ? 1 : RW;
+  const int row_bytes = (ksplit ? Kdim / 4 : Kdim) * (int)sizeof(T);   // bytes one stream covers
+  const int full_row_bytes = Kdim * (int)sizeof(T);
+  const int nseg = (row_bytes + SEG - 1) / SEG;
+  const int groups = (Rdim + rows_per_unit - 1) / rows_per_unit;
+  const int total_units = (*p.n_act) * groups;
   if (gw >= total_units) return;
 
   if (lane == 0) {
@@ -82,13 +89,13 @@ __global__ void __launch_bounds__(S::THREADS, 1) ffn_gemv_kernel(FfnParams p, Sl
     Unit q;
     const int e = p.act_list[u / groups];
     const ExpertPtrs ep = p.experts[st.slot[e]];
-    q.r0 = (u % groups) * RW;
+    q.r0 = (u % groups) * rows_per_unit;
     q.pos0 = p.offsets[e];
     q.n = p.offsets[e + 1] - q.pos0;
     const int sidx = lane & 3;
-    const int row = min(q.r0 + (DUAL ? (sidx & 1) : sidx), Rdim - 1);
+    const int row = min(q.r0 + (DUAL ? (sidx & 1) : (ksplit ? 0 : sidx)), Rdim - 1);
     const void* base = DUAL ? ep.w[sidx >> 1] : ep.w[2];
-    q.row = reinterpret_cast<const unsigned char*>(base) + (size_t)row * row_bytes;
+    q.row = reinterpret_cast<const unsigned char*>(base) + (size_t)row * full_row_bytes + (ksplit ? (size_t)sidx * row_bytes : 0);
     return q;
   };
 
@@ -156,22 +163,40 @@ __global__ void __launch_bounds__(S::THREADS, 1) ffn_gemv_kernel(FfnParams p, Sl
             wc.from_smem(sbase + (size_t)s * SEG + (size_t)cl * CB);
             wc.unpack(wf[s]);
           }
+          if (!ksplit) {
 #pragma unroll
-          for (int tt = 0; tt < NT; ++tt) {
-            Chunk<T> xc;
-            xc.template load<false>(xr[tt] + (size_t)seg * SEG_ELEMS + (size_t)cl * 8);
-            float xf[8];
-            xc.unpack(xf);
+            for (int tt = 0; tt < NT; ++tt) {
+              Chunk<T> xc;
+              xc.template load<false>(xr[tt] + (size_t)seg * SEG_ELEMS + (size_t)cl * 8);
+              float xf[8];
+              xc.unpack(xf);
+#pragma unroll
+              for (int s = 0; s < 4; ++s)
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[s][tt] = fmaf(wf[s][i], xf[i], acc[s][tt]);
+            }
+          } else {
 #pragma unroll
             for (int s = 0; s < 4; ++s)
 #pragma unroll
-              for (int i = 0; i < 8; ++i) acc[s][tt] = fmaf(wf[s][i], xf[i], acc[s][tt]);
+              for (int tt = 0; tt < NT; ++tt) {
+                Chunk<T> xc;
+                xc.template load<false>(xr[tt] + (size_t)s * (Kdim / 4) + (size_t)seg * SEG_ELEMS + (size_t)cl * 8);
+                float xf[8];
+                xc.unpack(xf);
+#pragma unroll
+                for (int i = 0; i < 8; ++i) acc[s][tt] = fmaf(wf[s][i], xf[i], acc[s][tt]);
+              }
           }
         }
         __syncwarp();   // every lane is done with the slot before it is refilled
       }
       if (dead) break;
 
+      if (ksplit) {
+#pragma unroll
+        for (int tt = 0; tt < NT; ++tt) acc[0][tt] = (acc[0][tt] + acc[1][tt]) + (acc[2][tt] + acc[3][tt]);
+      }
 #pragma unroll
       for (int s = 0; s < 4; ++s)
 #pragma unroll
@@ -196,7 +221,7 @@ __global__ void __launch_bounds__(S::THREADS, 1) ffn_gemv_kernel(FfnParams p, Sl
         for (int rr = 0; rr < 4; ++rr)
 #pragma unroll
           for (int tt = 0; tt < NT; ++tt) {
-            if (lane == rr * NT + tt && tt < nt && cq.r0 + rr < Rdim)
+            if (lane == rr * NT + tt && tt < nt && cq.r0 + rr < Rdim && rr < rows_per_unit)
               reinterpret_cast<T*>(p.y)[(size_t)(cq.pos0 + c0 + tt) * p.H + cq.r0 + rr] = Elem<T>::from_float(acc[rr][tt]);
           }
       }
@@ -210,6 +235,8 @@ __global__ void __launch_bounds__(S::THREADS, 1) ffn_gemv_kernel(FfnParams p, Sl
 // exactly where the reference's `final_output[tok] += expert_output * weights` rounds.
 // ---------------------------------------------------------------------------------------------
 struct CombineParams {
+  const float* ypart;   // K-split down projection: fp32 slices [y_parts][pairs_cap][H], else null
+  int y_parts, pairs_cap;
   const void* y;        // [pairs, H] sorted-pair order
   const int* inv;       // [T*K]
   const int64_t* ids64; // [T,K]
@@ -299,7 +326,7 @@ template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine
       for (int u = 0; u < 4; ++u) {
         if (j0 + u < n) {
           const int k = s_order[j0 + u];
-          yc[u].template load<false>(y + (size_t)s_pos[k] * p.H + c * 8);
+          if (p.ypart == nullptr) yc[u].template load<false>(y + (size_t)s_pos[k] * p.H + c * 8);
           w[u] = s_w[k];
         }
       }
@@ -307,7 +334,22 @@ template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine
       for (int u = 0; u < 4; ++u) {
         if (j0 + u < n) {
           float yf[8];
-          yc[u].unpack(yf);
+          if (p.ypart == nullptr) {
+            yc[u].unpack(yf);
+          } else {
+            // the down projection's value is the sum of its K slices, added in slice order and
+            // rounded to the model dtype once - the rounding point of the reference's F.linear
+            const float* src = p.ypart + (size_t)s_pos[s_order[j0 + u]] * p.H + c * 8;
+            float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
+            yf[0] = a.x; yf[1] = a.y; yf[2] = a.z; yf[3] = a.w; yf[4] = b.x; yf[5] = b.y; yf[6] = b.z; yf[7] = b.w;
+            for (int sl = 1; sl < p.y_parts; ++sl) {
+              const float* q = src + (size_t)sl * p.pairs_cap * p.H;
+              a = __ldg(reinterpret_cast<const float4*>(q)); b = __ldg(reinterpret_cast<const float4*>(q) + 1);
+              yf[0] += a.x; yf[1] += a.y; yf[2] += a.z; yf[3] += a.w; yf[4] += b.x; yf[5] += b.y; yf[6] += b.z; yf[7] += b.w;
+            }
+#pragma unroll
+            for (int i = 0; i < 8; ++i) yf[i] = rn<T>(yf[i]);
+          }
 #pragma unroll
           for (int i = 0; i < 8; ++i) {
             // __fmul_rn / __fadd_rn are never contracted into an FMA: the reference multiplies, then adds

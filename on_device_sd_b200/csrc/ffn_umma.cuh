@@ -51,6 +51,12 @@ struct UmmaParams {
   FfnParams f;
   const CUtensorMap* tmaps;   // [E][3] for this layer: gate (box 64x64), up (64x64), down (64x128)
   int* status;
+  // Down projection only: K split into `ksplit` slices so that few experts still give every SM
+  // several work items.  Slice s writes fp32 partial sums to ypart[s][pos][H]; the combine kernel
+  // adds the slices in index order (deterministic) and rounds once.  ksplit == 1: bf16 y as usual.
+  int ksplit;
+  float* ypart;
+  int pairs_cap;              // rows of one slice of ypart
 };
 
 // ---- PTX wrappers -------------------------------------------------------------------------
@@ -148,7 +154,15 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   // weight stream starts immediately and only the loaders (readers of h) wait for gate/up to finish.
   if (DUAL) pdl_wait();
   pdl_trigger();
-  const int total = (*p.n_act) * tiles;
+  const int KS = DUAL ? 1 : up.ksplit;
+  const int total = (*p.n_act) * tiles * KS;
+  // work item -> (expert slot in act_list, row tile, K slice); k-blocks [kb0, kb1) of the slice
+#define B200MOE_DECODE_ITEM(item)                                   \
+  const int ks_ = (item) % KS;                                      \
+  const int tile = ((item) / KS) % tiles;                           \
+  const int e = p.act_list[(item) / KS / tiles];                    \
+  const int kb0 = ks_ * nkb / KS, kb1 = (ks_ + 1) * nkb / KS;       \
+  (void)tile; (void)kb0; (void)kb1;
 
   if (threadIdx.x == 0) {
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1 + kUmmaLoaders); mbar_init(&empty[i], 1); }
@@ -174,8 +188,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
       uint32_t ph = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-        const int e = p.act_list[item / tiles];
-        const int tile = item % tiles;
+        B200MOE_DECODE_ITEM(item)
         const int slot = st.slot[e];
         const int n = p.offsets[e + 1] - p.offsets[e];
         const CUtensorMap* m0 = up.tmaps + (size_t)slot * 3 + (DUAL ? 0 : 2);
@@ -183,7 +196,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
         tensormap_acquire(m0);
         if (DUAL) tensormap_acquire(m1);
         for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
-          for (int kb = 0; kb < nkb; ++kb) {
+          for (int kb = kb0; kb < kb1; ++kb) {
             if (!wait_or_abort(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
             mbar_expect_tx(&full[s], kUmmaATile);
             unsigned char* dst = As + (size_t)s * kUmmaATile;
@@ -206,7 +219,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
       uint32_t ph = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-        const int e = p.act_list[item / tiles];
+        B200MOE_DECODE_ITEM(item)
         const int n = p.offsets[e + 1] - p.offsets[e];
         for (int c0 = 0; c0 < n && ok; c0 += NMAX, ++job) {
           const int npad = (min(NMAX, n - c0) + 15) & ~15;
@@ -215,14 +228,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
           if (!wait_or_abort(&acc_empty[b], ((job >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)(b * NMAX);
-          for (int kb = 0; kb < nkb; ++kb) {
+          for (int kb = kb0; kb < kb1; ++kb) {
             if (!wait_or_abort(&full[s], ph, abort_flag)) { ok = false; break; }
             tc_fence_after();
             const uint64_t adesc = umma_desc_sw128(smem_addr(As + (size_t)s * kUmmaATile));
             const uint64_t bdesc = umma_desc_sw128(smem_addr(Bs + (size_t)s * B_TILE));
 #pragma unroll
             for (int k = 0; k < kUmmaBK / 16; ++k)   // 32 bytes of K per instruction: +2 in the 16-byte address field
-              tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+              tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
             tc_commit(&empty[s]);      // frees the stage when these MMAs have read it
             if (++s == STAGES) { s = 0; ph ^= 1; }
           }
@@ -239,7 +252,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
     uint32_t ph = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total; item += gridDim.x) {   // runs to the end even after a failed wait: the named barriers below need all 128 threads
-      const int e = p.act_list[item / tiles];
+      B200MOE_DECODE_ITEM(item)
       const int pos0 = p.offsets[e];
       const int n = p.offsets[e + 1] - pos0;
       for (int c0 = 0; c0 < n; c0 += NMAX) {
@@ -253,7 +266,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
                             : reinterpret_cast<const __nv_bfloat16*>(p.h) + (size_t)pos * p.I;
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
-        for (int kb = 0; kb < nkb && ok; ++kb) {
+        for (int kb = kb0; kb < kb1 && ok; ++kb) {
           if (!wait_or_abort(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
           unsigned char* bt = Bs + (size_t)s * B_TILE;
           for (int id = tl; id < npad * 8; id += kUmmaLoaders) {
@@ -291,8 +304,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
     __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h);
     __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(p.y);
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-      const int e = p.act_list[item / tiles];
-      const int tile = item % tiles;
+      B200MOE_DECODE_ITEM(item)
       const int pos0 = p.offsets[e];
       const int n = p.offsets[e + 1] - pos0;
       for (int c0 = 0; c0 < n && ok; c0 += NMAX, ++job) {
@@ -335,8 +347,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
             const int grow = tile * 128 + q * 32 + lane;
 #pragma unroll
             for (int j = 0; j < 16; ++j)
-              if (col + j < nt && grow < Rdim)
-                yout[(size_t)(pos0 + c0 + col + j) * p.H + grow] = __float2bfloat16_rn(__uint_as_float(r[j]));
+              if (col + j < nt && grow < Rdim) {
+                if (KS > 1) up.ypart[((size_t)ks_ * up.pairs_cap + (pos0 + c0 + col + j)) * p.H + grow] = __uint_as_float(r[j]);
+                else yout[(size_t)(pos0 + c0 + col + j) * p.H + grow] = __float2bfloat16_rn(__uint_as_float(r[j]));
+              }
           }
         }
         tc_fence_before();
@@ -353,5 +367,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
     asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"((uint32_t)S::TMEM_COLS) : "memory");
   }
 }
+
+#undef B200MOE_DECODE_ITEM
 
 }  // namespace b200moe
