@@ -35,16 +35,16 @@ struct RouterParams {
 
 template <typename T> __device__ __forceinline__ double exact_dot(const T* xr, const T* wr, int nch, int lane) {
   double acc = 0.0;
-  for (int c0 = lane; c0 < nch; c0 += 128) {
-    Chunk<T> xc[4], wc[4];
+  for (int c0 = lane; c0 < nch; c0 += 256) {
+    Chunk<T> xc[8], wc[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       const int c = c0 + 32 * u;
       if (c < nch) { xc[u].template load<false>(xr + c * 8); wc[u].template load<false>(wr + c * 8); }
       else { xc[u].zero(); wc[u].zero(); }
     }
 #pragma unroll
-    for (int u = 0; u < 4; ++u) {
+    for (int u = 0; u < 8; ++u) {
       float xf[8], wf[8];
       xc[u].unpack(xf);
       wc[u].unpack(wf);
