@@ -23,6 +23,7 @@
 #include "router.cuh"
 #ifdef B200MOE_WITH_INT4
 #include "ffn_int4.cuh"
+#include "ffn_int4_umma.cuh"
 #endif
 #ifdef B200MOE_WITH_UMMA
 #include "ffn_umma.cuh"
@@ -47,6 +48,8 @@ struct b200moe_ctx {
   std::vector<CUtensorMap> h_tmaps;
   std::vector<uint8_t> tmap_ok;
   CUtensorMap* d_tmaps = nullptr;
+  std::vector<CUtensorMap> h_tmaps2;   // int4 only: second set of boxes (tcgen05 int4 kernel)
+  CUtensorMap* d_tmaps2 = nullptr;
   void* encode_fn = nullptr;   // cuTensorMapEncodeTiled, resolved through the runtime
 #endif
   // workspace
@@ -61,6 +64,7 @@ struct b200moe_ctx {
   int* n_act = nullptr;
   void* h = nullptr;
   void* y = nullptr;
+  void* xperm = nullptr;            // int4 tcgen05 path: k-permuted copy of the layer input [Tm,H]
   float* ypart = nullptr;           // fp32 K-slices of the down projection (tensor-core path)
   int ypart_slices = 0;             // slices ypart has room for
   int last_ksplit = 1;              // K split used by the most recent tensor-core launch
@@ -221,6 +225,21 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
   if (cfg->act_dtype == B200MOE_BF16) {   // dense bf16 (tcgen05 path) and int4 (TMA boxes of packed nibbles)
     ctx->h_tmaps.assign((L * E + 1) * 3, CUtensorMap{});
     ctx->tmap_ok.assign(L * E + 1, 0);
+    if (cfg->weight_mode == B200MOE_W_INT4_G128) {
+      char* xp = nullptr;
+      if ((rc = dev_alloc(ctx, &xp, Tm * (size_t)H * 2))) {
+        std::string msg = ctx->err;
+        b200moe_destroy(ctx);
+        return fail(nullptr, rc, "%s", msg.c_str());
+      }
+      ctx->xperm = xp;
+      ctx->h_tmaps2.assign((L * E + 1) * 3, CUtensorMap{});
+      if ((rc = dev_alloc(ctx, &ctx->d_tmaps2, (L * E + 1) * 3))) {
+        std::string msg = ctx->err;
+        b200moe_destroy(ctx);
+        return fail(nullptr, rc, "%s", msg.c_str());
+      }
+    }
     if ((rc = dev_alloc(ctx, &ctx->d_tmaps, (L * E + 1) * 3))) {
       std::string msg = ctx->err;
       b200moe_destroy(ctx);
@@ -313,14 +332,15 @@ static bool encode_map(b200moe_ctx* ctx, CUtensorMap* out, const void* base, int
 }
 
 // packed int4 matrix, uint8 [rows, bytes_per_row] -> 2-D map with a {128 bytes, 16 rows} box, 128-byte swizzle
-static bool encode_map_u8(b200moe_ctx* ctx, CUtensorMap* out, const void* base, int rows, int bytes_per_row) {
+static bool encode_map_u8(b200moe_ctx* ctx, CUtensorMap* out, const void* base, int rows, int bytes_per_row, int box_bytes = 128,
+                          int box_rows = 16) {
   if (!ctx->encode_fn) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)bytes_per_row, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)bytes_per_row};
-  const cuuint32_t box[2] = {128u, 16u};
+  const cuuint32_t box[2] = {(cuuint32_t)box_bytes, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1u, 1u};
   CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_fn)(out, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<void*>(base), dims, strides, box,
-                                                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                                                               estr, CU_TENSOR_MAP_INTERLEAVE_NONE, box_bytes == 64 ? CU_TENSOR_MAP_SWIZZLE_64B : CU_TENSOR_MAP_SWIZZLE_128B,
                                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
 }
@@ -370,7 +390,14 @@ extern "C" int b200moe_set_expert(b200moe_ctx* ctx, int layer, int expert, const
 #ifdef B200MOE_WITH_UMMA
   if (!ctx->h_tmaps.empty()) {
     const size_t idx = (size_t)layer * E + expert;
-    ctx->tmap_ok[idx] = encode_expert_maps(ctx, &ctx->h_tmaps[idx * 3], gate_proj, up_proj, down_proj) ? 1 : 0;
+    bool ok = encode_expert_maps(ctx, &ctx->h_tmaps[idx * 3], gate_proj, up_proj, down_proj);
+    if (ok && !ctx->h_tmaps2.empty()) {   // 128 k x 64/128 rows boxes for the tcgen05 int4 kernel
+      const int H0 = ctx->cfg.hidden_size, I0 = ctx->cfg.intermediate_size;
+      CUtensorMap* m = &ctx->h_tmaps2[idx * 3];
+      ok = encode_map_u8(ctx, &m[0], gate_proj, I0, H0 / 2, 64, 64) && encode_map_u8(ctx, &m[1], up_proj, I0, H0 / 2, 64, 64) &&
+           encode_map_u8(ctx, &m[2], down_proj, H0, I0 / 2, 64, 128);
+    }
+    ctx->tmap_ok[idx] = ok ? 1 : 0;
   }
 #endif
   return B200MOE_OK;
@@ -480,6 +507,9 @@ static int upload_layer_table(b200moe_ctx* ctx, int layer, cudaStream_t st) {
   if (!ctx->h_tmaps.empty())
     CUDA_TRY(ctx, cudaMemcpyAsync(ctx->d_tmaps + (size_t)layer * E * 3, ctx->h_tmaps.data() + (size_t)layer * E * 3,
                                   (size_t)E * 3 * sizeof(CUtensorMap), cudaMemcpyHostToDevice, st));
+  if (!ctx->h_tmaps2.empty())
+    CUDA_TRY(ctx, cudaMemcpyAsync(ctx->d_tmaps2 + (size_t)layer * E * 3, ctx->h_tmaps2.data() + (size_t)layer * E * 3,
+                                  (size_t)E * 3 * sizeof(CUtensorMap), cudaMemcpyHostToDevice, st));
 #endif
   ctx->dirty[layer] = 0;
   return B200MOE_OK;
@@ -496,7 +526,9 @@ struct FfnLaunch {
   void* y;
   int K;        // pairs per token in sorted_pair
   const void* tmaps;  // tensor maps matching `experts` (null when the tensor-core path cannot run)
+  const void* tmaps2 = nullptr;  // int4: boxes of the tcgen05 int4 kernel
   int max_n;    // upper bound on tokens per expert
+  int n_tokens = 0;      // rows of x (only the int4 tcgen05 path needs it)
   int n_act_bound = 1;   // upper bound on the number of experts with work
   bool ksplit_ok = false;   // the consumer of y accepts fp32 K-slices (the combine kernel does)
 };
@@ -611,6 +643,49 @@ template <int NTILE> static int launch_int4_pair(b200moe_ctx* ctx, const Int4Par
   return post_launch(ctx, "ffn_int4_kernel<down>");
 }
 
+template <int NMAX> static int launch_i4u_pair(b200moe_ctx* ctx, const I4uParams& ip, const SlotTable& st, cudaStream_t s) {
+  using S = I4uShape<NMAX>;
+  auto k_up = ffn_int4_umma_kernel<NMAX, true>;
+  auto k_down = ffn_int4_umma_kernel<NMAX, false>;
+  static bool configured = false;
+  if (!configured) {
+    CUDA_TRY(ctx, cudaFuncSetAttribute(k_up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
+    CUDA_TRY(ctx, cudaFuncSetAttribute(k_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
+    configured = true;
+  }
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
+    launch_chain(k_up, dim3(ctx->sm_count), dim3(kI4uThreads), S::SMEM, s, ip, st);
+  }
+  int rc = post_launch(ctx, "ffn_int4_umma_kernel<gate/up>");
+  if (rc) return rc;
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_FFN_DOWN, s);
+    launch_chain(k_down, dim3(ctx->sm_count), dim3(kI4uThreads), S::SMEM, s, ip, st);
+  }
+  return post_launch(ctx, "ffn_int4_umma_kernel<down>");
+}
+
+static int launch_ffn_int4_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tmaps, const SlotTable& st, int max_n, int n_tokens,
+                                cudaStream_t s) {
+  I4uParams ip{};
+  ip.f = p;
+  ip.tmaps = reinterpret_cast<const CUtensorMap*>(tmaps);
+  ip.status = ctx->status;
+  ip.xperm = ctx->xperm;
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_PERMUTE, s);
+    launch_chain(i4u_permute_x_kernel, dim3(std::min(4 * ctx->sm_count, std::max(1, n_tokens))), dim3(256), 0, s,
+                 reinterpret_cast<const __nv_bfloat16*>(p.x), reinterpret_cast<__nv_bfloat16*>(ctx->xperm), n_tokens, p.H);
+  }
+  int rc0 = post_launch(ctx, "i4u_permute_x_kernel");
+  if (rc0) return rc0;
+  if (max_n <= 16) return launch_i4u_pair<16>(ctx, ip, st, s);
+  if (max_n <= 32) return launch_i4u_pair<32>(ctx, ip, st, s);
+  if (max_n <= 64) return launch_i4u_pair<64>(ctx, ip, st, s);
+  return launch_i4u_pair<128>(ctx, ip, st, s);
+}
+
 static int launch_ffn_int4(b200moe_ctx* ctx, const FfnParams& p, const void* tmaps, const SlotTable& st, int max_n, cudaStream_t s) {
   if (!tmaps) return fail(ctx, B200MOE_E_STATE, "int4 path: no TMA descriptors for these experts (cuTensorMapEncodeTiled unavailable or failed)");
   Int4Params ip{};
@@ -631,6 +706,13 @@ static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st,
   p.H = c.hidden_size; p.I = c.intermediate_size; p.K = f.K;
   if (c.weight_mode == B200MOE_W_INT4_G128) {
 #ifdef B200MOE_WITH_INT4
+    // Measured on B200: the register-fragment kernel wins while experts hold few tokens; the tcgen05
+    // kernel (token count rides N for free, but its bf16 A tiles cost shared-memory round trips) wins
+    // for few large experts with >= 12 tokens each (Mixtral-shaped, T = 64: 0.48 ms against 0.61 ms).
+    const long long n_avg = (long long)f.n_tokens * c.top_k / std::max(1, c.num_experts);
+    const bool prefer_umma = n_avg >= 12 && c.hidden_size >= 4096;
+    if (f.tmaps2 && ffn_kind != B200MOE_FFN_GEMV && (ffn_kind == B200MOE_FFN_MMA || prefer_umma))
+      return launch_ffn_int4_umma(ctx, p, f.tmaps2, st, f.max_n, f.n_tokens, s);
     return launch_ffn_int4(ctx, p, f.tmaps, st, f.max_n, s);
 #else
     return fail(ctx, B200MOE_E_UNSUPPORTED, "library built without the int4 kernels");
@@ -689,6 +771,7 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   f.experts = ctx->d_experts + (size_t)layer * E;
   f.offsets = ctx->offsets; f.sorted_pair = ctx->sorted_pair; f.act_list = ctx->act_list; f.n_act = ctx->n_act;
   f.x = x; f.h = ctx->h; f.y = ctx->y; f.K = c.top_k; f.max_n = T;
+  f.n_tokens = T;
   f.n_act_bound = (int)std::min<long long>(E, (long long)T * c.top_k);
   f.ksplit_ok = scores != nullptr;   // the expert-parallel scatter reads bf16 y
   ctx->last_ksplit = 1;
@@ -698,6 +781,7 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
     for (int e = 0; e < E; ++e)
       if (tab.slot[e] >= 0 && !ctx->tmap_ok[(size_t)layer * E + tab.slot[e]]) all_ok = false;
     if (all_ok) f.tmaps = ctx->d_tmaps + (size_t)layer * E * 3;
+    if (all_ok && ctx->d_tmaps2) f.tmaps2 = ctx->d_tmaps2 + (size_t)layer * E * 3;
   }
 #endif
   if ((rc = launch_ffn(ctx, f, tab, ffn_kind, st))) return rc;

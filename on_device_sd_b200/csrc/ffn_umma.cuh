@@ -113,8 +113,8 @@ __device__ __forceinline__ uint32_t umma_idesc_bf16(int n) {
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
-    if ((i & 255u) == 255u) {
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;   // sleeps up to 20 us per poll, woken by the barrier
+    if ((i & 15u) == 15u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > (1ll << 31)) { *abort_flag = 1; return false; }
     }
@@ -127,7 +127,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   constexpr int STAGES = S::STAGES;
   constexpr int B_TILE = S::B_TILE;
   constexpr int TILE_ROWS = DUAL ? 64 : 128;       // output rows per tile
-  constexpr int LOADER_LAG = 2;                    // cp.async groups a loader keeps in flight
+  constexpr int LOADER_LAG = (STAGES >= 8) ? 4 : 2;  // cp.async groups a loader keeps in flight
   static_assert(STAGES > LOADER_LAG + 1, "ring too shallow");
   const FfnParams& p = up.f;
   extern __shared__ unsigned char smem_dyn[];

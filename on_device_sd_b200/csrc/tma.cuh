@@ -30,13 +30,26 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
       : "memory");
   return ok != 0;
 }
+// try_wait with a suspend-time hint: the warp is descheduled until the phase completes or the
+// hint (nanoseconds) runs out, instead of burning issue slots that the working warps need.
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parity, uint32_t ns) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(smem_addr(bar)), "r"(parity), "r"(ns)
+      : "memory");
+  return ok != 0;
+}
 // Waits for the phase with the given parity, but never forever: after kSpinLimit failed polls
 // (each poll itself blocks for a hardware-defined slice) it gives up and returns false; the
 // caller records the failure in the status word and leaves.
 constexpr uint32_t kSpinLimit = 1u << 22;
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
   for (uint32_t i = 0; i < kSpinLimit; ++i)
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
   return false;
 }
 

@@ -56,13 +56,16 @@ def _int4_layer(H, E, K, I, T, seed):
     return L, ctx, deq
 
 
+@pytest.mark.parametrize("kind", ["gemv", "mma"])
 @pytest.mark.parametrize("T", [1, 5, 8, 20, 40])
-def test_int4_moe_matches_oracle_on_dequantised_weights(T):
+def test_int4_moe_matches_oracle_on_dequantised_weights(T, kind):
     """The oracle for int4 is the reference forward on dequant(quant(W)); K = 384 exercises a last
     TMA box that is half beyond the matrix, I = 136... is not allowed (multiples of 128), so rows use 16-row tails via H."""
     H, E, K, I = 384, 8, 2, 256
     L, ctx, deq = _int4_layer(H, E, K, I, T, seed=21)
-    out, ids, scores = ctx.forward_fused(0, L.x.cuda(), return_routing=True)
+    from on_device_sd_b200 import FFN_GEMV, FFN_MMA
+    # "gemv": per-warp tiles with register-fragment MMAs (any token count); "mma": the tcgen05 kernel
+    out, ids, scores = ctx.forward_fused(0, L.x.cuda(), return_routing=True, ffn_kind={"gemv": FFN_GEMV, "mma": FFN_MMA}[kind])
     assert ctx.status() == 0
     o_ids, o_sc, _ = O.route(L.x, L.gate_w, K)
     assert torch.equal(ids.cpu(), o_ids)
@@ -79,12 +82,14 @@ def test_int4_qwen3_shape_reduced_experts(T):
     _close(out, want, torch.bfloat16, tight=True)
 
 
-def test_int4_all_tokens_one_expert_many_passes():
-    H, E, K, I, T = 256, 4, 2, 128, 100
+@pytest.mark.parametrize("kind", ["gemv", "mma"])
+def test_int4_all_tokens_one_expert_many_passes(kind):
+    from on_device_sd_b200 import FFN_GEMV, FFN_MMA
+    H, E, K, I, T = 256, 4, 2, 128, 200
     L, ctx, deq = _int4_layer(H, E, K, I, T, seed=23)
     ids = torch.tensor([[2, 0]] * T)
     sc = torch.softmax(torch.randn(T, K, generator=torch.Generator().manual_seed(2)), -1).bfloat16()
-    out = ctx.forward(0, L.x.cuda(), ids.cuda(), sc.cuda())
+    out = ctx.forward(0, L.x.cuda(), ids.cuda(), sc.cuda(), ffn_kind={"gemv": FFN_GEMV, "mma": FFN_MMA}[kind])
     assert ctx.status() == 0
     _close(out, O.moe_engine(L.x, ids, sc, deq, order=[0, 2]), torch.bfloat16, tight=True)
 
