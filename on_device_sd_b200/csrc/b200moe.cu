@@ -64,7 +64,7 @@ struct b200moe_ctx {
   int* n_act = nullptr;
   void* h = nullptr;
   void* y = nullptr;
-  void* xperm = nullptr;            // int4 tcgen05 path: k-permuted copy of the layer input [Tm,H]
+  void* xperm = nullptr;            // int4 tcgen05 path: k-permuted token rows in sorted-pair order [Tm*K, H]
   float* ypart = nullptr;           // fp32 K-slices of the down projection (tensor-core path)
   int ypart_slices = 0;             // slices ypart has room for
   int last_ksplit = 1;              // K split used by the most recent tensor-core launch
@@ -227,7 +227,7 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
     ctx->tmap_ok.assign(L * E + 1, 0);
     if (cfg->weight_mode == B200MOE_W_INT4_G128) {
       char* xp = nullptr;
-      if ((rc = dev_alloc(ctx, &xp, Tm * (size_t)H * 2))) {
+      if ((rc = dev_alloc(ctx, &xp, pairs * (size_t)H * 2))) {
         std::string msg = ctx->err;
         b200moe_destroy(ctx);
         return fail(nullptr, rc, "%s", msg.c_str());
@@ -643,7 +643,7 @@ template <int NTILE> static int launch_int4_pair(b200moe_ctx* ctx, const Int4Par
   return post_launch(ctx, "ffn_int4_kernel<down>");
 }
 
-template <int NMAX> static int launch_i4u_pair(b200moe_ctx* ctx, const I4uParams& ip, const SlotTable& st, cudaStream_t s) {
+template <int NMAX> static int launch_i4u_pair(b200moe_ctx* ctx, const I4uParams& ip_up, const I4uParams& ip_down, const SlotTable& st, cudaStream_t s) {
   using S = I4uShape<NMAX>;
   auto k_up = ffn_int4_umma_kernel<NMAX, true>;
   auto k_down = ffn_int4_umma_kernel<NMAX, false>;
@@ -655,35 +655,41 @@ template <int NMAX> static int launch_i4u_pair(b200moe_ctx* ctx, const I4uParams
   }
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
-    launch_chain(k_up, dim3(ctx->sm_count), dim3(kI4uThreads), S::SMEM, s, ip, st);
+    launch_chain(k_up, dim3(ctx->sm_count), dim3(kI4uThreads), S::SMEM, s, ip_up, st);
   }
   int rc = post_launch(ctx, "ffn_int4_umma_kernel<gate/up>");
   if (rc) return rc;
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_DOWN, s);
-    launch_chain(k_down, dim3(ctx->sm_count), dim3(kI4uThreads), S::SMEM, s, ip, st);
+    launch_chain(k_down, dim3(ctx->sm_count), dim3(kI4uThreads), S::SMEM, s, ip_down, st);
   }
   return post_launch(ctx, "ffn_int4_umma_kernel<down>");
 }
 
 static int launch_ffn_int4_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tmaps, const SlotTable& st, int max_n, int n_tokens,
                                 cudaStream_t s) {
-  I4uParams ip{};
-  ip.f = p;
-  ip.tmaps = reinterpret_cast<const CUtensorMap*>(tmaps);
-  ip.status = ctx->status;
-  ip.xperm = ctx->xperm;
+  const size_t pairs_cap = (size_t)ctx->cfg.max_tokens * ctx->cfg.top_k;
+  I4uParams ip_up{}, ip_down{};
+  ip_up.f = p;
+  ip_up.tmaps = reinterpret_cast<const CUtensorMap*>(tmaps);
+  ip_up.status = ctx->status;
+  ip_down = ip_up;
+  // token rows of the two passes as TMA tensors: the gathered copy of x, and h
+  if (!encode_map(ctx, &ip_up.bmap, ctx->xperm, (int)pairs_cap, p.H, 16) || !encode_map(ctx, &ip_down.bmap, p.h, (int)pairs_cap, p.I, 16))
+    return fail(ctx, B200MOE_E_STATE, "int4 tensor-core path: cuTensorMapEncodeTiled failed for the token tiles");
   {
     ProfScope prof(ctx, B200MOE_KERNEL_PERMUTE, s);
-    launch_chain(i4u_permute_x_kernel, dim3(std::min(4 * ctx->sm_count, std::max(1, n_tokens))), dim3(256), 0, s,
-                 reinterpret_cast<const __nv_bfloat16*>(p.x), reinterpret_cast<__nv_bfloat16*>(ctx->xperm), n_tokens, p.H);
+    const long long chunks = (long long)n_tokens * p.K * (p.H / 8);
+    const int grid = (int)std::min<long long>(4LL * ctx->sm_count, std::max<long long>(1, (chunks + 255) / 256));
+    launch_chain(i4u_gather_x_kernel, dim3(grid), dim3(256), 0, s, reinterpret_cast<const __nv_bfloat16*>(p.x),
+                 reinterpret_cast<__nv_bfloat16*>(ctx->xperm), p.sorted_pair, p.offsets, ctx->cfg.num_experts, p.K, p.H);
   }
-  int rc0 = post_launch(ctx, "i4u_permute_x_kernel");
+  int rc0 = post_launch(ctx, "i4u_gather_x_kernel");
   if (rc0) return rc0;
-  if (max_n <= 16) return launch_i4u_pair<16>(ctx, ip, st, s);
-  if (max_n <= 32) return launch_i4u_pair<32>(ctx, ip, st, s);
-  if (max_n <= 64) return launch_i4u_pair<64>(ctx, ip, st, s);
-  return launch_i4u_pair<128>(ctx, ip, st, s);
+  if (max_n <= 16) return launch_i4u_pair<16>(ctx, ip_up, ip_down, st, s);
+  if (max_n <= 32) return launch_i4u_pair<32>(ctx, ip_up, ip_down, st, s);
+  if (max_n <= 64) return launch_i4u_pair<64>(ctx, ip_up, ip_down, st, s);
+  return launch_i4u_pair<128>(ctx, ip_up, ip_down, st, s);
 }
 
 static int launch_ffn_int4(b200moe_ctx* ctx, const FfnParams& p, const void* tmaps, const SlotTable& st, int max_n, cudaStream_t s) {

@@ -1,21 +1,33 @@
 // K3d - grouped SwiGLU expert FFN over int4 g128 weights on the tcgen05 tensor cores.
 // Same contract and numerics as ffn_int4.cuh (the dequantised weight is bf16(scale * q), bit for
-// bit), but the tokens ride the MMA's N dimension, so the per-weight work no longer grows with the
-// number of tokens an expert holds: used for batches of two or more tokens.
+// bit), but the tokens ride the MMA's N dimension, so the per-weight work does not grow with the
+// number of tokens an expert holds.
 //
 // Data flow per stage of 128 k (= one scale group):
-//   TMA box (128 rows x 64 bytes of nibbles, 64-byte swizzle) -> shared-memory ring (8 stages)
-//   -> 8 dequant warps: thread (row, half) reads 32 bytes, converts 64 nibbles in registers
-//      (lop3 magic, exact subtraction, one bf16 multiplication by the group scale) and stores them
-//      as the bf16 A tile of the MMA in the canonical 128-byte-swizzle layout (two 64-k atoms)
-//   -> tcgen05.mma (A and B from shared memory, accumulator in TMEM), epilogue as in ffn_umma.cuh.
-// lop3 extracts nibble pairs (t, t+4); instead of re-ordering the weights, the tokens carry the
-// same permutation inside every group of 8 k: a small kernel writes a permuted copy of x once per
-// call, and the gate/up epilogue stores h permuted, so the loader warps stay plain cp.async.
+//   TMA box (128 rows x 64 bytes of nibbles, 64-byte swizzle) -> shared-memory ring
+//   -> dequant warps: thread (row, half) reads 32 bytes, converts 64 nibbles in registers
+//      (lop3 magic, exact subtraction, one bf16 multiplication by the group scale) and writes them
+//      with tcgen05.st into TENSOR MEMORY: lane = weight row, 32 columns = 64 k.  The dequantised
+//      tile never touches shared memory - a bf16 copy there would cost eight times the packed
+//      bytes in shared-memory traffic (write + read).
+//   -> tcgen05.mma with A from tensor memory and B (tokens) from shared memory, accumulator in
+//      tensor memory, epilogue as in ffn_umma.cuh.
+// Tensor memory (512 columns): accumulators 2 x PARTS x NMAX at column 0, A ring 4 x 64 columns at 256.
 //
-//   warp 0      TMA producer            warp 1      MMA issuer + TMEM owner
-//   warps 2-5   token-tile loaders      warps 6-13  dequant
-//   warps 14-17 epilogue
+// Token tiles also arrive by TMA: a small kernel first writes the tokens of every (token, expert)
+// pair in sorted-pair order - so an expert's rows are contiguous, like the rows of h - with the k
+// permutation the nibble extraction wants (lop3 yields pairs (t, t+4); every group of 8 k is
+// stored as k0,k4,k1,k5,k2,k6,k3,k7, and the gate/up epilogue stores h the same way).  A tile is
+// then a few plain {64 k, 16 rows} boxes; rows past the expert's last token belong to the next expert
+// and only feed accumulator columns nobody reads.  No thread computes addresses per 16 bytes:
+// the integer pipe is what bounds this kernel (7 ALU operations per 8 weights for the nibbles).
+//
+//   warp 0      TMA producer, weights   warp 1      MMA issuer (even k-stages) + TMEM owner
+//   warp 2      TMA producer, tokens    warp 3      MMA issuer (odd k-stages)
+//   warps 4-19  dequant: four groups of 4 warps; group g owns A stage g, i.e. every fourth k-stage,
+//               thread = one weight row of the stage (64 bytes of nibbles -> 64 columns)
+//   warps 20-23 epilogue
+// Producer and issuer warps run warp-uniform with one elected lane per instruction (see tc_mma_bf16_w).
 #pragma once
 #include <cuda.h>
 
@@ -26,36 +38,45 @@
 
 namespace b200moe {
 
-constexpr int kI4uThreads = 18 * 32;
-constexpr int kI4uLoaders = 128;
-constexpr int kI4uDequant = 256;
-constexpr int kI4uWStages = 6;            // ring of packed tiles (8 KB each): the bytes in flight from HBM
+constexpr int kI4uDeqGroups = 4;                  // = number of A stages: group g always fills stage g
+constexpr int kI4uDeqWarps = 4 * kI4uDeqGroups;   // per group: one warp per TMEM lane quarter
+constexpr int kI4uFirstDeq = 4;
+constexpr int kI4uFirstEpi = kI4uFirstDeq + kI4uDeqWarps;
+constexpr int kI4uThreads = (kI4uFirstEpi + 4) * 32;
 constexpr int kI4uWTile = 128 * 64;       // 128 rows x 64 bytes = 128 k of nibbles
-constexpr int kI4uATile = 2 * 16384;      // bf16 A tile: two atoms of 128 rows x 128 bytes
 constexpr int kI4uBK = 128;
+constexpr int kI4uAStages = 4;            // dequantised A tiles in tensor memory
+constexpr int kI4uACols = 64;             // 128 k of bf16 = 64 32-bit columns per lane
+constexpr int kI4uACol0 = 256;            // first column of the A ring (accumulators sit below)
 
-// Shared memory: the packed-tile ring, the bf16 A ring (32 KB per stage, few stages) and a separate,
-// deeper ring for the small token tiles - the token tiles come from L2 with cp.async and need
-// several stages in flight to hide that latency.
+// Shared memory: the packed-tile ring (the bytes in flight from HBM) and a ring of token tiles.
 template <int NMAX> struct I4uShape {
-  static constexpr int B_TILE = 2 * NMAX * 128;                 // two 64-k atoms
-  static constexpr int A_STAGES = NMAX <= 32 ? 4 : (NMAX == 64 ? 3 : 2);
+  static constexpr int B_TILE = 2 * NMAX * 128;                 // two 64-k atoms of NMAX rows x 128 bytes
+  static constexpr int W_STAGES = NMAX <= 64 ? 12 : 8;          // 8 KB each; a multiple of the number of dequant groups
+  static constexpr int A_STAGES = kI4uAStages;
   static constexpr int EX_BYTES = 64 * 17 * 4;
-  static constexpr int PTR_BYTES = 128 * 8;
-  static constexpr int FIXED = 1024 + kI4uWStages * kI4uWTile + A_STAGES * kI4uATile + EX_BYTES + PTR_BYTES + 512;
+  static constexpr int FIXED = 1024 + W_STAGES * kI4uWTile + EX_BYTES + 512;
   static constexpr int B_FIT = (227 * 1024 - FIXED) / B_TILE;
   static constexpr int B_STAGES = B_FIT > 8 ? 8 : B_FIT;
-  static constexpr int LOADER_LAG = B_STAGES >= 6 ? 4 : (B_STAGES - 2 > 0 ? B_STAGES - 2 : 1);
   static constexpr size_t SMEM = (size_t)FIXED + (size_t)B_STAGES * B_TILE;
-  static constexpr int TMEM_COLS = (2 * NMAX) < 32 ? 32 : 2 * NMAX;
+  static constexpr int TMEM_COLS = 512;
+  // Successive MMAs into one accumulator serialise on its latency, so the k-steps rotate over
+  // PARTS independent accumulators that the epilogue adds up.
+  static constexpr int PARTS = NMAX <= 32 ? 4 : (NMAX == 64 ? 2 : 1);
+  // One warp issues a tcgen05.mma every 45-150 cycles depending on how the operands reach the
+  // uniform registers, the tensor pipe takes one every ~38: two issuing warps (even / odd k-stages,
+  // disjoint accumulators) keep the eight MMAs of a stage inside the stage's HBM time.
+  static constexpr int MMA_WARPS = PARTS >= 2 ? 2 : 1;
+  static constexpr int PARTS_PER_WARP = PARTS / MMA_WARPS;
+  static_assert(2 * PARTS * NMAX <= kI4uACol0, "accumulators overlap the A ring");
   static_assert(B_STAGES >= 3, "token tile too large for the shared-memory budget");
 };
 
 struct I4uParams {
   FfnParams f;
-  const void* xperm;          // [T,H] copy of x with every group of 8 k stored as k0,k4,k1,k5,k2,k6,k3,k7
   const CUtensorMap* tmaps;   // [E][3]: uint8 maps with {64 B, 64 rows} (gate, up) / {64 B, 128 rows} (down) boxes, 64-byte swizzle
   int* status;
+  CUtensorMap bmap;           // token rows of this pass in sorted-pair order ([pairs, H] or [pairs, I] bf16), box {64 k, 16 rows}, 128-byte swizzle
 };
 
 // 8 nibbles -> 4 words holding (q_t, q_{t+4}) * scale as bf16 pairs, t = 0..3 (see ffn_int4.cuh)
@@ -70,24 +91,60 @@ __device__ __forceinline__ void i4u_dequant8(uint32_t w, __nv_bfloat162 scale2, 
   }
 }
 
+// D[tmem] (+)= A[tmem] * B[smem]: the A operand is read from tensor memory (lane = row of A).
+// Called by a converged warp, one elected lane issues (see tc_mma_bf16_w).
+__device__ __forceinline__ void tc_mma_bf16_ts_w(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\telect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+// 32 consecutive 32-bit columns of this thread's lane
+__device__ __forceinline__ void tc_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+  asm volatile(
+      "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, %16, "
+      "%17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31, %32};"
+      ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]), "r"(r[9]),
+        "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]),
+        "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]),
+        "r"(r[30]), "r"(r[31]) : "memory");
+}
+__device__ __forceinline__ void tc_wait_st() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
+// Called by a converged warp: one elected lane arms the barrier / issues the copy.
+__device__ __forceinline__ void mbar_expect_tx_w(uint64_t* bar, uint32_t bytes) {
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+               "@q mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(smem_addr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_w(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar, uint64_t policy) {
+  asm volatile(
+      "{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+      "@q cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes.L2::cache_hint [%0], [%1, {%2, %3}], [%4], %5;\n\t}"
+      ::"r"(smem_addr(dst)), "l"(map), "r"(c0), "r"(c1), "r"(smem_addr(bar)), "l"(policy)
+      : "memory");
+}
+__device__ __forceinline__ uint64_t l2_policy_evict_last() {
+  uint64_t pol;
+  asm volatile("createpolicy.fractional.L2::evict_last.b64 %0, 1.0;" : "=l"(pol));
+  return pol;
+}
+
 template <int NMAX, bool DUAL>
-__global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(I4uParams ip, SlotTable st) {
+__global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __grid_constant__ I4uParams ip, SlotTable st) {
   using S = I4uShape<NMAX>;
-  constexpr int STAGES = S::A_STAGES;       // bf16 A ring
+  constexpr int STAGES = S::A_STAGES;       // A ring in tensor memory
   constexpr int BSTAGES = S::B_STAGES;      // token-tile ring
+  constexpr int WSTAGES = S::W_STAGES;      // packed-tile ring
   constexpr int B_TILE = S::B_TILE;
   constexpr int TILE_ROWS = DUAL ? 64 : 128;
   const FfnParams& p = ip.f;
   extern __shared__ unsigned char smem_dyn[];
   unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_dyn) + 1023) & ~(uintptr_t)1023);
   unsigned char* Ws = smem;                                           // packed tiles
-  unsigned char* As = Ws + (size_t)kI4uWStages * kI4uWTile;          // bf16 A tiles
-  unsigned char* Bs = As + (size_t)STAGES * kI4uATile;               // token tiles
+  unsigned char* Bs = Ws + (size_t)WSTAGES * kI4uWTile;              // token tiles
   float* ex = reinterpret_cast<float*>(Bs + (size_t)BSTAGES * B_TILE);
-  const __nv_bfloat16** rowptr = reinterpret_cast<const __nv_bfloat16**>(reinterpret_cast<unsigned char*>(ex) + S::EX_BYTES);
-  uint64_t* w_full = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(rowptr) + S::PTR_BYTES);
-  uint64_t* w_empty = w_full + kI4uWStages;
-  uint64_t* full = w_empty + kI4uWStages;     // A stage written by the dequant warps
+  uint64_t* w_full = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(ex) + S::EX_BYTES);
+  uint64_t* w_empty = w_full + WSTAGES;
+  uint64_t* full = w_empty + WSTAGES;          // A stage written by the dequant warps
   uint64_t* empty = full + STAGES;
   uint64_t* b_full = empty + STAGES;           // token tile landed
   uint64_t* b_empty = b_full + BSTAGES;
@@ -103,15 +160,15 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(I4uParams
   const int tiles = (Rdim + TILE_ROWS - 1) / TILE_ROWS;
   const int sgroups = Kdim / 128;
 
-  if (DUAL) pdl_wait();
+  if (DUAL) pdl_wait();                          // the token copy of the gather kernel must be complete
   pdl_trigger();
   const int total = (*p.n_act) * tiles;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < kI4uWStages; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], kI4uDequant); }
-    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], kI4uDequant); mbar_init(&empty[i], 1); }
-    for (int i = 0; i < BSTAGES; ++i) { mbar_init(&b_full[i], kI4uLoaders); mbar_init(&b_empty[i], 1); }
-    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
+    for (int i = 0; i < WSTAGES; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], 4); }
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 4); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < BSTAGES; ++i) { mbar_init(&b_full[i], 1); mbar_init(&b_empty[i], 1); }
+    for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], S::MMA_WARPS); mbar_init(&acc_empty[i], 128); }
     *abort_flag = 0;
     mbar_fence_init();
     fence_proxy_async();
@@ -126,131 +183,120 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(I4uParams
   const uint32_t tmem_base = *tmem_holder;
 
   if (warp == 0) {
-    // ------------------------------ TMA producer: packed tiles ------------------------------
-    if (lane == 0) {
-      const uint64_t policy = l2_policy_evict_first();
-      int s = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-        const int e = p.act_list[item / tiles];
-        const int tile = item % tiles;
-        const int slot = st.slot[e];
-        const int n = p.offsets[e + 1] - p.offsets[e];
-        const CUtensorMap* m0 = ip.tmaps + (size_t)slot * 3 + (DUAL ? 0 : 2);
-        const CUtensorMap* m1 = ip.tmaps + (size_t)slot * 3 + 1;
-        tensormap_acquire(m0);
-        if (DUAL) tensormap_acquire(m1);
-        for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
-          for (int kb = 0; kb < nkb; ++kb) {
-            if (!wait_or_abort(&w_empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
-            mbar_expect_tx(&w_full[s], kI4uWTile);
-            unsigned char* dst = Ws + (size_t)s * kI4uWTile;
-            if (DUAL) {
-              tma_load_2d(dst, m0, kb * 64, tile * 64, &w_full[s], policy);
-              tma_load_2d(dst + 4096, m1, kb * 64, tile * 64, &w_full[s], policy);
-            } else {
-              tma_load_2d(dst, m0, kb * 64, tile * 128, &w_full[s], policy);
-            }
-            if (++s == kI4uWStages) { s = 0; ph ^= 1; }
-          }
-        }
-      }
-      if (!ok) atomicOr(ip.status, kDevWaitExpired);
-    }
-  } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      int s = 0, sb = 0, job = 0;
-      uint32_t ph = 0, phb = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-        const int e = p.act_list[item / tiles];
-        const int n = p.offsets[e + 1] - p.offsets[e];
-        for (int c0 = 0; c0 < n && ok; c0 += NMAX, ++job) {
-          const int npad = (min(NMAX, n - c0) + 15) & ~15;
-          const uint32_t idesc = umma_idesc_bf16(npad);
-          const int b = job & 1;
-          if (!wait_or_abort(&acc_empty[b], ((job >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
-          tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)(b * NMAX);
-          for (int kb = 0; kb < nkb; ++kb) {
-            if (!wait_or_abort(&full[s], ph, abort_flag) || !wait_or_abort(&b_full[sb], phb, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-#pragma unroll
-            for (int atom = 0; atom < 2; ++atom) {
-              const uint64_t adesc = umma_desc_sw128(smem_addr(As + (size_t)s * kI4uATile + atom * 16384));
-              const uint64_t bdesc = umma_desc_sw128(smem_addr(Bs + (size_t)sb * B_TILE + atom * NMAX * 128));
-#pragma unroll
-              for (int k = 0; k < 4; ++k)
-                tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > 0 || atom > 0 || k > 0) ? 1u : 0u);
-            }
-            tc_commit(&empty[s]);
-            tc_commit(&b_empty[sb]);
-            if (++s == STAGES) { s = 0; ph ^= 1; }
-            if (++sb == BSTAGES) { sb = 0; phb ^= 1; }
-          }
-          if (ok) tc_commit(&acc_full[b]);
-        }
-      }
-      if (!ok) atomicOr(ip.status, kDevWaitExpired);
-    }
-  } else if (warp < 6) {
-    // ------------------------------ token-tile loaders (cp.async, inputs already k-permuted) ------------------------------
-    const int tl = threadIdx.x - 64;          // 0..127
-    constexpr int LOADER_LAG = S::LOADER_LAG;
-    if (!DUAL) pdl_wait();                    // h must be complete
-    int s = 0, lag_s = 0, issued = 0;
+    // ------------------------------ TMA producer: packed weight tiles (whole warp, one elected lane issues) ------------------------------
+    const uint64_t policy = l2_policy_evict_first();
+    int s = 0;
     uint32_t ph = 0;
     bool ok = true;
-    for (int item = blockIdx.x; item < total; item += gridDim.x) {   // runs to the end even after a failed wait (named barriers)
-      const int e = p.act_list[item / tiles];
-      const int pos0 = p.offsets[e];
-      const int n = p.offsets[e + 1] - pos0;
-      for (int c0 = 0; c0 < n; c0 += NMAX) {
-        const int nt = min(NMAX, n - c0);
-        const int npad = (nt + 15) & ~15;
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        if (tl < npad) {
-          const int pos = pos0 + c0 + min(tl, nt - 1);
-          rowptr[tl] = DUAL ? reinterpret_cast<const __nv_bfloat16*>(ip.xperm) + (size_t)(p.sorted_pair[pos] / p.K) * p.H
-                            : reinterpret_cast<const __nv_bfloat16*>(p.h) + (size_t)pos * p.I;
-        }
-        asm volatile("bar.sync 2, 128;" ::: "memory");
-        for (int kb = 0; kb < nkb && ok; ++kb) {
-          if (!wait_or_abort(&b_empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
-          unsigned char* bt = Bs + (size_t)s * B_TILE;
-          for (int id = tl; id < npad * 16; id += kI4uLoaders) {
-            const int r = id >> 4, c = id & 15;           // chunk c of 16: atom c>>3, 16-byte slot c&7
-            const bool live = r < nt;
-            const __nv_bfloat16* src = rowptr[r];
-            cp_async_16(bt + (c >> 3) * NMAX * 128 + r * 128 + (((c & 7) ^ (r & 7)) << 4),
-                        live ? (const void*)(src + kb * kI4uBK + c * 8) : (const void*)src, live ? 16u : 0u);
+    for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+      const int e = warp_bcast(p.act_list[item / tiles]);
+      const int tile = item % tiles;
+      const int slot = st.slot[e];
+      const int n = warp_bcast(p.offsets[e + 1] - p.offsets[e]);
+      const CUtensorMap* m0 = ip.tmaps + (size_t)slot * 3 + (DUAL ? 0 : 2);
+      const CUtensorMap* m1 = ip.tmaps + (size_t)slot * 3 + 1;
+      tensormap_acquire(m0);
+      if (DUAL) tensormap_acquire(m1);
+      for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!__all_sync(0xffffffffu, wait_or_abort(&w_empty[s], ph ^ 1, abort_flag))) { ok = false; break; }
+          mbar_expect_tx_w(&w_full[s], kI4uWTile);
+          unsigned char* dst = Ws + (size_t)s * kI4uWTile;
+          if (DUAL) {
+            tma_load_2d_w(dst, m0, kb * 64, tile * 64, &w_full[s], policy);
+            tma_load_2d_w(dst + 4096, m1, kb * 64, tile * 64, &w_full[s], policy);
+          } else {
+            tma_load_2d_w(dst, m0, kb * 64, tile * 128, &w_full[s], policy);
           }
-          cp_async_commit();
-          ++issued;
-          if (issued > LOADER_LAG) {
-            cp_async_wait<LOADER_LAG>();
-            fence_proxy_async();
-            mbar_arrive(&b_full[lag_s]);
-            if (++lag_s == BSTAGES) lag_s = 0;
+          if (++s == WSTAGES) { s = 0; ph ^= 1; }
+        }
+      }
+    }
+    if (!ok && lane == 0) atomicOr(ip.status, kDevWaitExpired);
+  } else if (warp == 2) {
+    // ------------------------------ TMA producer: token tiles ------------------------------
+    const uint64_t policy = l2_policy_evict_last();      // every CTA working on this expert re-reads these rows
+    if (!DUAL) pdl_wait();                               // h must be complete; the weight stream above has already started
+    int s = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+      const int e = warp_bcast(p.act_list[item / tiles]);
+      const int pos0 = warp_bcast(p.offsets[e]);
+      const int n = warp_bcast(p.offsets[e + 1]) - pos0;
+      for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
+        for (int kb = 0; kb < nkb; ++kb) {
+          if (!__all_sync(0xffffffffu, wait_or_abort(&b_empty[s], ph ^ 1, abort_flag))) { ok = false; break; }
+          const int npad = (min(NMAX, n - c0) + 15) & ~15;
+          mbar_expect_tx_w(&b_full[s], (uint32_t)(2 * npad * 128));
+          unsigned char* dst = Bs + (size_t)s * B_TILE;
+          for (int r = 0; r < npad; r += 16) {   // boxes of 16 rows: only the rows this pass multiplies are fetched
+            tma_load_2d_w(dst + r * 128, &ip.bmap, kb * kI4uBK, pos0 + c0 + r, &b_full[s], policy);
+            tma_load_2d_w(dst + NMAX * 128 + r * 128, &ip.bmap, kb * kI4uBK + 64, pos0 + c0 + r, &b_full[s], policy);
           }
           if (++s == BSTAGES) { s = 0; ph ^= 1; }
         }
       }
     }
-    cp_async_wait<0>();
-    fence_proxy_async();
-    for (int q = min(issued, LOADER_LAG); q > 0; --q) {
-      mbar_arrive(&b_full[lag_s]);
-      if (++lag_s == BSTAGES) lag_s = 0;
+    if (!ok && lane == 0) atomicOr(ip.status, kDevWaitExpired);
+  } else if (warp == 1 || warp == 3) {
+    // ------------------------------ MMA issuers (whole warps, warp-uniform; see tc_mma_bf16_w) ------------------------------
+    // Issuer w takes the k-stages of a job with kb % MMA_WARPS == w and owns PARTS_PER_WARP accumulators.
+    const int w = warp == 1 ? 0 : 1;
+    if (w < S::MMA_WARPS) {
+      int s = 0, sb = 0, job = 0;
+      uint32_t ph = 0, phb = 0;
+      bool ok = true;
+      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+        const int e = p.act_list[item / tiles];
+        const int n = warp_bcast(p.offsets[e + 1] - p.offsets[e]);
+        for (int c0 = 0; c0 < n && ok; c0 += NMAX, ++job) {
+          const int npad = (min(NMAX, n - c0) + 15) & ~15;
+          const uint32_t idesc = umma_idesc_bf16(npad);
+          const int b = job & 1;
+          if (!__all_sync(0xffffffffu, wait_or_abort(&acc_empty[b], ((job >> 1) & 1) ^ 1, abort_flag))) { ok = false; break; }
+          tc_fence_after();
+          const uint32_t d_tmem = tmem_base + (uint32_t)((b * S::PARTS + w * S::PARTS_PER_WARP) * NMAX);
+          for (int kb = 0; kb < nkb; ++kb) {
+            if ((kb % S::MMA_WARPS) == w) {
+              const bool got = wait_or_abort(&full[s], ph, abort_flag) && wait_or_abort(&b_full[sb], phb, abort_flag);
+              if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
+              tc_fence_after();
+              const uint32_t a_tmem = tmem_base + (uint32_t)(kI4uACol0 + s * kI4uACols);
+              const uint32_t first = kb < S::MMA_WARPS ? 0u : 1u;      // this issuer's first stage of the job starts its accumulators
+#pragma unroll
+              for (int atom = 0; atom < 2; ++atom) {
+                const uint64_t bdesc = umma_desc_sw128(smem_addr(Bs + (size_t)sb * B_TILE + atom * NMAX * 128));
+#pragma unroll
+                for (int k = 0; k < 4; ++k) {   // 16 k per MMA = 8 columns of A
+                  const int kk = atom * 4 + k;
+                  tc_mma_bf16_ts_w(d_tmem + (uint32_t)((kk % S::PARTS_PER_WARP) * NMAX), a_tmem + (uint32_t)(kk * 8), bdesc + 2 * k, idesc,
+                                   kk >= S::PARTS_PER_WARP ? 1u : first);
+                }
+              }
+              tc_commit_w(&empty[s]);
+              tc_commit_w(&b_empty[sb]);
+            }
+            if (++s == STAGES) { s = 0; ph ^= 1; }
+            if (++sb == BSTAGES) { sb = 0; phb ^= 1; }
+          }
+          if (ok) tc_commit_w(&acc_full[b]);
+        }
+      }
+      if (!ok && lane == 0) atomicOr(ip.status, kDevWaitExpired);
     }
-    if (!ok && tl == 0) atomicOr(ip.status, kDevWaitExpired);
-  } else if (warp < 14) {
-    // ------------------------------ dequant: packed tile -> bf16 A tile ------------------------------
-    const int dt = threadIdx.x - 192;         // 0..255
-    const int row = dt & 127, half = dt >> 7; // row of the tile, which 64 k of the 128
-    int ws = 0, s = 0;
+  } else if (warp < kI4uFirstEpi) {
+    // ------------------------------ dequant: packed tile -> bf16 A tile in tensor memory ------------------------------
+    // A warp may only touch the 32 TMEM lanes of its quarter (warp % 4): thread = weight row of the stage.
+    // Group grp handles the k-stages whose running index is grp modulo 4 and therefore always A stage grp.
+    static_assert(kI4uDeqGroups == kI4uAStages && WSTAGES % kI4uDeqGroups == 0, "group <-> stage mapping");
+    const int q = warp & 3;
+    const int row = q * 32 + lane, grp = (warp - kI4uFirstDeq) >> 2;
+    const int sw = (row >> 1) & 3;              // 64-byte swizzle of the TMA box: 16-byte slot c of row r sits at c ^ ((r >> 1) & 3)
+    const unsigned char* wrow0 = Ws + row * 64;
+    const uint32_t a_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kI4uACol0 + grp * kI4uACols);
+    int ws = grp;                                 // packed-ring slot of this group's next stage
+    int first = grp;                              // first k-stage of the next job that belongs to this group
     uint32_t wph = 0, ph = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
@@ -268,39 +314,52 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(I4uParams
         sc = reinterpret_cast<const __nv_bfloat16*>(ep.s[2]) + (size_t)gr * sgroups;
       }
       for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
-        __nv_bfloat16 sv = sc[0];
-        for (int kb = 0; kb < nkb; ++kb) {
-          const __nv_bfloat16 sv_next = sc[min(kb + 1, nkb - 1)];   // next group's scale, fetched a stage ahead
-          if (!wait_or_abort(&w_full[ws], wph, abort_flag)) { ok = false; break; }
-          // 64-byte swizzle of the TMA box: 16-byte slot c of row r sits at c ^ ((r >> 1) & 3)
-          const unsigned char* wrow = Ws + (size_t)ws * kI4uWTile + row * 64;
-          const int sw = (row >> 1) & 3;
-          const uint4 q0 = *reinterpret_cast<const uint4*>(wrow + (((half * 2 + 0) ^ sw) << 4));
-          const uint4 q1 = *reinterpret_cast<const uint4*>(wrow + (((half * 2 + 1) ^ sw) << 4));
-          mbar_arrive(&w_empty[ws]);
-          if (++ws == kI4uWStages) { ws = 0; wph ^= 1; }
-          if (!wait_or_abort(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
-          unsigned char* arow = As + (size_t)s * kI4uATile + half * 16384 + row * 128;
-          const __nv_bfloat162 s2 = __nv_bfloat162(sv, sv);
-          const uint32_t words[8] = {q0.x, q0.y, q0.z, q0.w, q1.x, q1.y, q1.z, q1.w};
+        int kb = first;
+        for (; kb < nkb; kb += kI4uDeqGroups) {
+          const __nv_bfloat16 sv = sc[kb];
+          if (!__all_sync(0xffffffffu, wait_or_abort(&w_full[ws], wph, abort_flag))) { ok = false; break; }   // warp-uniform
+          const unsigned char* wrow = wrow0 + (size_t)ws * kI4uWTile;
+          uint4 pk[4];
 #pragma unroll
-          for (int c = 0; c < 8; ++c) {       // word c = 8 k = one 16-byte chunk of the bf16 row
-            uint32_t o[4];
-            i4u_dequant8(words[c], s2, o);
-            *reinterpret_cast<uint4*>(arow + ((c ^ (row & 7)) << 4)) = make_uint4(o[0], o[1], o[2], o[3]);
+          for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(wrow + ((c ^ sw) << 4));
+          __syncwarp();
+          if (lane == 0) mbar_arrive(&w_empty[ws]);
+          ws += kI4uDeqGroups;
+          if (ws >= WSTAGES) { ws -= WSTAGES; wph ^= 1; }
+          const __nv_bfloat162 s2 = __nv_bfloat162(sv, sv);
+          bool free_checked = false;
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {  // 64 k = 32 columns at a time keeps the register count down
+            const uint32_t words[8] = {pk[2 * half].x, pk[2 * half].y, pk[2 * half].z, pk[2 * half].w,
+                                       pk[2 * half + 1].x, pk[2 * half + 1].y, pk[2 * half + 1].z, pk[2 * half + 1].w};
+            uint32_t o[32];
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {         // word c = 8 k = 4 columns
+              uint32_t o4[4];
+              i4u_dequant8(words[c], s2, o4);
+              o[4 * c + 0] = o4[0]; o[4 * c + 1] = o4[1]; o[4 * c + 2] = o4[2]; o[4 * c + 3] = o4[3];
+            }
+            if (!free_checked) {
+              if (!__all_sync(0xffffffffu, wait_or_abort(&empty[grp], ph ^ 1, abort_flag))) { ok = false; break; }
+              tc_fence_after();
+              free_checked = true;
+            }
+            tc_st32(a_addr + (uint32_t)(half * 32), o);
           }
-          fence_proxy_async();
-          mbar_arrive(&full[s]);
-          if (++s == STAGES) { s = 0; ph ^= 1; }
-          sv = sv_next;
+          if (!ok) break;
+          tc_wait_st();
+          tc_fence_before();
+          if (lane == 0) mbar_arrive(&full[grp]);
+          ph ^= 1;
         }
+        first = kb - nkb;                         // the stride carries over into the next job
       }
     }
-    if (!ok && dt == 0) atomicOr(ip.status, kDevWaitExpired);
+    if (!ok && lane == 0) atomicOr(ip.status, kDevWaitExpired);
   } else {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;                       // TMEM lane quarter this warp may read
-    const int et = threadIdx.x - 448;             // 0..127
+    const int et = threadIdx.x - kI4uFirstEpi * 32;   // 0..127
     int job = 0;
     bool ok = true;
     __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h);
@@ -322,7 +381,17 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(I4uParams
         tc_fence_after();
         for (int col = 0; col < npad; col += 16) {
           uint32_t r[16];
-          tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NMAX + col), r);
+          tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * S::PARTS * NMAX + col), r);
+          // with a single k-stage the second issuer never started its accumulators
+          const int parts = (S::MMA_WARPS > 1 && nkb < S::MMA_WARPS) ? S::PARTS_PER_WARP : S::PARTS;
+#pragma unroll
+          for (int part = 1; part < S::PARTS; ++part) {
+            if (part >= parts) break;
+            uint32_t r2[16];
+            tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((b * S::PARTS + part) * NMAX + col), r2);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(r2[j])));
+          }
           if (DUAL) {
             if (q >= 2) {
               const int rr = (q - 2) * 32 + lane;
@@ -369,17 +438,22 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(I4uParams
   }
 }
 
-// x [T,H] -> copy with every group of 8 elements stored as (x0,x4,x1,x5,x2,x6,x3,x7)
-__global__ void i4u_permute_x_kernel(const __nv_bfloat16* x, __nv_bfloat16* xperm, int T, int H) {
+// Tokens of every (token, expert) pair in sorted-pair order, every group of 8 k stored as
+// (x0,x4,x1,x5,x2,x6,x3,x7): row pos of xg = x[sorted_pair[pos] / K].  One warp-sized slice of a row per step.
+__global__ void i4u_gather_x_kernel(const __nv_bfloat16* x, __nv_bfloat16* xg, const int* sorted_pair, const int* offsets, int E, int K, int H) {
   pdl_wait();
   pdl_trigger();
-  const size_t nchunks = (size_t)T * (H / 8);
+  const int pairs = offsets[E];
+  const int chunks = H / 8;
+  const size_t nchunks = (size_t)pairs * chunks;
   for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < nchunks; i += (size_t)gridDim.x * blockDim.x) {
-    const uint4 v = ldg_cached(x + i * 8);
+    const int pos = (int)(i / chunks), c = (int)(i % chunks);
+    const int tok = sorted_pair[pos] / K;
+    const uint4 v = ldg_cached(x + (size_t)tok * H + c * 8);
     uint4 o;
     o.x = __byte_perm(v.x, v.z, 0x5410); o.y = __byte_perm(v.x, v.z, 0x7632);
     o.z = __byte_perm(v.y, v.w, 0x5410); o.w = __byte_perm(v.y, v.w, 0x7632);
-    *reinterpret_cast<uint4*>(xperm + i * 8) = o;
+    *reinterpret_cast<uint4*>(xg + (size_t)pos * H + c * 8) = o;
   }
 }
 

@@ -44,7 +44,11 @@ template <int NMAX> struct UmmaShape {
   static constexpr int EX_BYTES = 64 * 17 * 4;
   static constexpr int PTR_BYTES = 128 * 8;
   static constexpr size_t SMEM = 1024 /*alignment slack*/ + (size_t)STAGES * STAGE + EX_BYTES + PTR_BYTES + (2 * STAGES + 4) * 8 + 64;
-  static constexpr int TMEM_COLS = (2 * NMAX) < 32 ? 32 : 2 * NMAX;
+  // Successive MMAs into one accumulator serialise on its latency (about 170 cycles each, far more
+  // than a 128 x N x 16 product with a small N takes), so the k-steps rotate over PARTS independent
+  // accumulators that the epilogue adds up.
+  static constexpr int PARTS = NMAX <= 64 ? 4 : 2;
+  static constexpr int TMEM_COLS = 2 * PARTS * NMAX;            // 128, 256, 512, 512: powers of two
 };
 
 struct UmmaParams {
@@ -87,6 +91,23 @@ __device__ __forceinline__ void tc_mma_bf16(uint32_t d_tmem, uint64_t adesc, uin
       ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
       : "memory");
 }
+// The same two instructions for a CONVERGED warp: every lane executes the call, one elected lane
+// issues.  tcgen05.mma takes its descriptors from uniform registers; issued from a single-thread
+// branch each instruction measured 152 cycles on B200 (operands moved over one by one), from a
+// converged warp 44 (M = 128, N = 16), so the MMA warps keep their control flow warp-uniform.
+__device__ __forceinline__ void tc_commit_w(uint64_t* bar) {
+  asm volatile("{\n\t.reg .pred q;\n\telect.sync _|q, 0xffffffff;\n\t"
+               "@q tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(smem_addr(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_mma_bf16_w(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\tsetp.ne.b32 p, %4, 0;\n\telect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+      : "memory");
+}
+// lane 0's value in every lane; also tells the compiler the value is warp-uniform
+__device__ __forceinline__ int warp_bcast(int v) { return __shfl_sync(0xffffffffu, v, 0); }
 __device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
   asm volatile(
       "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
@@ -109,11 +130,17 @@ __device__ __forceinline__ uint32_t umma_idesc_bf16(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
 }
 
-// Bounded wait that also leaves when another role has raised the CTA's abort flag.
+// Bounded wait that also leaves when another role has raised the CTA's abort flag.  The first
+// probe costs one instruction; after that the warp sleeps between probes - a spinning warp takes
+// issue slots and integer-pipe cycles from the warps that do the work (measured on the int4 kernel:
+// almost half of all issued instructions were polls), and the clock is only read when the barrier
+// was found busy.
 __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, volatile int* abort_flag) {
+  if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
   const long long t0 = clock64();
   for (uint32_t i = 0;; ++i) {
-    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;   // sleeps up to 20 us per poll, woken by the barrier
+    __nanosleep(i < 8u ? 32u : 128u);
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
     if ((i & 15u) == 15u) {
       if (*abort_flag) return false;
       if (clock64() - t0 > (1ll << 31)) { *abort_flag = 1; return false; }
@@ -165,7 +192,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   (void)tile; (void)kb0; (void)kb1;
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1 + kUmmaLoaders); mbar_init(&empty[i], 1); }
+    for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1 + kUmmaLoaders / 32);   /* TMA bytes + one arrival per loader warp */ mbar_init(&empty[i], 1); }
     for (int i = 0; i < 2; ++i) { mbar_init(&acc_full[i], 1); mbar_init(&acc_empty[i], 128); }
     *abort_flag = 0;
     mbar_fence_init();
@@ -213,37 +240,35 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
       if (!ok) atomicOr(up.status, kDevWaitExpired);
     }
   } else if (warp == 1) {
-    // ------------------------------ MMA issuer ------------------------------
-    if (lane == 0) {
-      int s = 0, job = 0;
-      uint32_t ph = 0;
-      bool ok = true;
-      for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
-        B200MOE_DECODE_ITEM(item)
-        const int n = p.offsets[e + 1] - p.offsets[e];
-        for (int c0 = 0; c0 < n && ok; c0 += NMAX, ++job) {
-          const int npad = (min(NMAX, n - c0) + 15) & ~15;
-          const uint32_t idesc = umma_idesc_bf16(npad);
-          const int b = job & 1;
-          if (!wait_or_abort(&acc_empty[b], ((job >> 1) & 1) ^ 1, abort_flag)) { ok = false; break; }
+    // ------------------------------ MMA issuer (whole warp, warp-uniform; see tc_mma_bf16_w) ------------------------------
+    int s = 0, job = 0;
+    uint32_t ph = 0;
+    bool ok = true;
+    for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
+      B200MOE_DECODE_ITEM(item)
+      const int n = warp_bcast(p.offsets[e + 1] - p.offsets[e]);
+      for (int c0 = 0; c0 < n && ok; c0 += NMAX, ++job) {
+        const int npad = (min(NMAX, n - c0) + 15) & ~15;
+        const uint32_t idesc = umma_idesc_bf16(npad);
+        const int b = job & 1;
+        if (!__all_sync(0xffffffffu, wait_or_abort(&acc_empty[b], ((job >> 1) & 1) ^ 1, abort_flag))) { ok = false; break; }
+        tc_fence_after();
+        const uint32_t d_tmem = tmem_base + (uint32_t)(b * S::PARTS * NMAX);
+        for (int kb = kb0; kb < kb1; ++kb) {
+          if (!__all_sync(0xffffffffu, wait_or_abort(&full[s], ph, abort_flag))) { ok = false; break; }
           tc_fence_after();
-          const uint32_t d_tmem = tmem_base + (uint32_t)(b * NMAX);
-          for (int kb = kb0; kb < kb1; ++kb) {
-            if (!wait_or_abort(&full[s], ph, abort_flag)) { ok = false; break; }
-            tc_fence_after();
-            const uint64_t adesc = umma_desc_sw128(smem_addr(As + (size_t)s * kUmmaATile));
-            const uint64_t bdesc = umma_desc_sw128(smem_addr(Bs + (size_t)s * B_TILE));
+          const uint64_t adesc = umma_desc_sw128(smem_addr(As + (size_t)s * kUmmaATile));
+          const uint64_t bdesc = umma_desc_sw128(smem_addr(Bs + (size_t)s * B_TILE));
 #pragma unroll
-            for (int k = 0; k < kUmmaBK / 16; ++k)   // 32 bytes of K per instruction: +2 in the 16-byte address field
-              tc_mma_bf16(d_tmem, adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
-            tc_commit(&empty[s]);      // frees the stage when these MMAs have read it
-            if (++s == STAGES) { s = 0; ph ^= 1; }
-          }
-          if (ok) tc_commit(&acc_full[b]);
+          for (int k = 0; k < kUmmaBK / 16; ++k)   // 32 bytes of K per instruction: +2 in the 16-byte address field
+            tc_mma_bf16_w(d_tmem + (uint32_t)((k % S::PARTS) * NMAX), adesc + 2 * k, bdesc + 2 * k, idesc, (kb > kb0 || k >= S::PARTS) ? 1u : 0u);
+          tc_commit_w(&empty[s]);      // frees the stage when these MMAs have read it
+          if (++s == STAGES) { s = 0; ph ^= 1; }
         }
+        if (ok) tc_commit_w(&acc_full[b]);
       }
-      if (!ok) atomicOr(up.status, kDevWaitExpired);
     }
+    if (!ok && lane == 0) atomicOr(up.status, kDevWaitExpired);
   } else if (warp < 6) {
     // ------------------------------ token-tile loaders ------------------------------
     const int tl = threadIdx.x - 64;          // 0..127
@@ -267,7 +292,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
-          if (!wait_or_abort(&empty[s], ph ^ 1, abort_flag)) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, wait_or_abort(&empty[s], ph ^ 1, abort_flag))) { ok = false; break; }
           unsigned char* bt = Bs + (size_t)s * B_TILE;
           for (int id = tl; id < npad * 8; id += kUmmaLoaders) {
             const int r = id >> 3, chunk = id & 7;
@@ -281,7 +306,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
           if (issued > LOADER_LAG) {              // the group issued LOADER_LAG stages ago has landed
             cp_async_wait<LOADER_LAG>();
             fence_proxy_async();
-            mbar_arrive(&full[lag_s]);
+            __syncwarp();                         // one arrival per warp: 128 arrivals on one barrier serialise for hundreds of cycles
+            if (lane == 0) mbar_arrive(&full[lag_s]);
             if (++lag_s == STAGES) lag_s = 0;
           }
           if (++s == STAGES) { s = 0; ph ^= 1; }
@@ -290,11 +316,12 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
     }
     cp_async_wait<0>();
     fence_proxy_async();
+    __syncwarp();
     for (int q = min(issued, LOADER_LAG); q > 0; --q) {
-      mbar_arrive(&full[lag_s]);
+      if (lane == 0) mbar_arrive(&full[lag_s]);
       if (++lag_s == STAGES) lag_s = 0;
     }
-    if (!ok && tl == 0) atomicOr(up.status, kDevWaitExpired);
+    if (!ok && lane == 0) atomicOr(up.status, kDevWaitExpired);
   } else {
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;                       // TMEM lane quarter this warp may read
@@ -320,7 +347,14 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
         tc_fence_after();
         for (int col = 0; col < npad; col += 16) {
           uint32_t r[16];
-          tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * NMAX + col), r);
+          tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * S::PARTS * NMAX + col), r);
+#pragma unroll
+          for (int part = 1; part < S::PARTS; ++part) {
+            uint32_t r2[16];
+            tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((b * S::PARTS + part) * NMAX + col), r2);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(r2[j])));
+          }
           if (DUAL) {
             // lanes 0-63 hold gate rows, lanes 64-127 the same rows of up: pair them through smem
             if (q >= 2) {

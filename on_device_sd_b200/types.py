@@ -4,7 +4,7 @@ the reference's engine and objects built here are interchangeable (duck typing).
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Any, Dict, Optional, Set
+from typing import Any, Dict, List, Optional, Set
 
 import torch
 
@@ -46,6 +46,23 @@ class AttentionOutput:
     hidden_states: torch.Tensor
     post_attn_normed: torch.Tensor
     residual: torch.Tensor
+
+
+@dataclass
+class ExpertActivation:
+    """demo/src/core/types.py:40-45."""
+    expert_id: Any
+    token_indices: torch.Tensor   # tokens that selected this expert at this rank, ascending
+    scores: torch.Tensor          # their routing weights
+    top_k_rank: int
+
+
+@dataclass
+class LayerExpertActivations:
+    """demo/src/core/types.py:48-52."""
+    layer_idx: int
+    activations: List[ExpertActivation]
+    routing_scores: torch.Tensor
 
 
 @dataclass

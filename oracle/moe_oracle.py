@@ -218,6 +218,19 @@ def activated_order(layer_idx: int, ids: torch.Tensor) -> List[int]:
     return [k.expert_idx for k in s]
 
 
+def layer_activations(ids: torch.Tensor, scores: torch.Tensor, num_experts: int) -> List[Tuple[int, int, torch.Tensor, torch.Tensor]]:
+    """(top_k_rank, expert, token_indices, scores) per non-empty (rank, expert) cell, in the order
+    demo/src/execution/model_runner_utils.py:21-35 appends ExpertActivation objects: rank outer,
+    expert inner, tokens from ``torch.where`` (ascending), scores ``topk_scores[tokens, k]``."""
+    out = []
+    for k in range(ids.shape[1]):
+        for e in range(num_experts):
+            tok = torch.where(ids[:, k] == e)[0]
+            if tok.numel():
+                out.append((k, e, tok, scores[tok, k]))
+    return out
+
+
 # --------------------------------------------------------------------------------------
 # expert FFN and the two MoE block paths
 # --------------------------------------------------------------------------------------

@@ -160,6 +160,23 @@ def main() -> None:
     np.savez_compressed(golden / "placement_fp16.npz", **rec)
     print("placement_fp16: substitution / skip / fp32-score semantics == reference bit for bit")
 
+    # LayerExpertActivations (demo/src/execution/model_runner_utils.py:13-41) on a routed batch
+    from src.execution.model_runner_utils import build_layer_activations
+    layer = make_layer(64, 16, 4, 32, torch.bfloat16, 40, seed=5)
+    with torch.no_grad():
+        ids, scores, _ = O.route(layer.x, layer.gate_w, 4)
+    ref_acts = build_layer_activations(RoutingResult(3, ids, scores, set()), 16)
+    mine = O.layer_activations(ids, scores, 16)
+    assert len(ref_acts.activations) == len(mine) and ref_acts.layer_idx == 3 and ref_acts.routing_scores is scores
+    for a, (k, e, tok, sc) in zip(ref_acts.activations, mine):
+        assert (a.top_k_rank, a.expert_id.expert_idx, a.expert_id.layer_idx) == (k, e, 3)
+        assert torch.equal(a.token_indices, tok) and torch.equal(a.scores, sc)
+    np.savez_compressed(golden / "activations_bf16.npz", ids=ids.numpy(), scores=to_np(scores), num_experts=16,
+                        rank=np.array([m[0] for m in mine]), expert=np.array([m[1] for m in mine]),
+                        count=np.array([m[2].numel() for m in mine]),
+                        tokens=torch.cat([m[2] for m in mine]).numpy(), act_scores=to_np(torch.cat([m[3] for m in mine])))
+    print(f"activations_bf16: {len(mine)} activations == reference")
+
     # int4 g128: the format is this build's; store a small packed example produced by the oracle
     g = torch.Generator().manual_seed(7)
     w = (torch.randn(24, 384, generator=g) * 0.02).to(torch.bfloat16)

@@ -71,3 +71,43 @@ def test_moe_shape_mirrors_config_dtype_rule():
     assert MoEShape(8, 2, 1, 8, "weird").get_dtype() == torch.float16   # demo/src/core/model.py:129 default
     a = AttentionOutput(torch.zeros(1), torch.zeros(1), torch.zeros(1))
     assert a.residual is not None
+
+
+def _check_activations(acts, want, layer_idx, scores):
+    assert acts.layer_idx == layer_idx and acts.routing_scores is scores
+    assert len(acts.activations) == len(want)
+    for a, (k, e, tok, sc) in zip(acts.activations, want):
+        assert (a.top_k_rank, a.expert_id.layer_idx, a.expert_id.expert_idx) == (k, layer_idx, e)
+        assert a.token_indices.dtype == torch.int64 and torch.equal(a.token_indices.cpu(), tok)
+        assert a.scores.dtype == scores.dtype and torch.equal(a.scores.cpu(), sc)
+
+
+def test_build_layer_activations_matches_reference_fixture():
+    """Fixture written from the reference's own build_layer_activations
+    (demo/src/execution/model_runner_utils.py:13-41): order, token lists and scores."""
+    import numpy as np
+    from conftest import GOLDEN, from_np
+    from on_device_sd_b200 import build_layer_activations
+    z = np.load(GOLDEN / "activations_bf16.npz")
+    ids = torch.from_numpy(z["ids"].astype(np.int64))
+    scores = from_np(z["scores"], torch.bfloat16)
+    acts = build_layer_activations(RoutingResult(3, ids, scores, set()), int(z["num_experts"]))
+    cuts = np.r_[0, np.cumsum(z["count"])]
+    toks, asc = torch.from_numpy(z["tokens"].astype(np.int64)), from_np(z["act_scores"], torch.bfloat16)
+    want = [(int(k), int(e), toks[a:b], asc[a:b]) for k, e, a, b in zip(z["rank"], z["expert"], cuts[:-1], cuts[1:])]
+    _check_activations(acts, want, 3, scores)
+
+
+def test_build_layer_activations_matches_oracle_on_random_and_edge_inputs():
+    from on_device_sd_b200 import build_layer_activations
+    g = torch.Generator().manual_seed(11)
+    for T, K, E in [(1, 1, 4), (7, 2, 8), (64, 8, 128), (33, 4, 5)]:
+        ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]) if K <= E else torch.randint(0, E, (T, K), generator=g)
+        scores = torch.rand(T, K, generator=g).to(torch.float16)
+        _check_activations(build_layer_activations(RoutingResult(1, ids, scores, set()), E), O.layer_activations(ids, scores, E), 1, scores)
+    # duplicates inside a token, ids outside [0, E) (never matched by the reference's comparison), empty batch
+    ids = torch.tensor([[0, 0], [5, 1], [-1, 2], [2, 2]])
+    scores = torch.rand(4, 2, generator=g)
+    _check_activations(build_layer_activations(RoutingResult(0, ids, scores, set()), 4), O.layer_activations(ids, scores, 4), 0, scores)
+    empty = build_layer_activations(RoutingResult(0, torch.zeros(0, 2, dtype=torch.int64), torch.zeros(0, 2), set()), 4)
+    assert empty.activations == []
