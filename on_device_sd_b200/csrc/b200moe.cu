@@ -527,7 +527,7 @@ struct FfnLaunch {
   int K;        // pairs per token in sorted_pair
   const void* tmaps;  // tensor maps matching `experts` (null when the tensor-core path cannot run)
   const void* tmaps2 = nullptr;  // int4: boxes of the tcgen05 int4 kernel
-  int max_n;    // upper bound on tokens per expert
+  int max_n;    // tokens per expert the kernels size their token tile for; experts holding more take several passes
   int n_tokens = 0;      // rows of x (only the int4 tcgen05 path needs it)
   int n_act_bound = 1;   // upper bound on the number of experts with work
   bool ksplit_ok = false;   // the consumer of y accepts fp32 K-slices (the combine kernel does)
@@ -712,12 +712,10 @@ static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st,
   p.H = c.hidden_size; p.I = c.intermediate_size; p.K = f.K;
   if (c.weight_mode == B200MOE_W_INT4_G128) {
 #ifdef B200MOE_WITH_INT4
-    // Measured on B200: the register-fragment kernel wins while experts hold few tokens; the tcgen05
-    // kernel (token count rides N for free, but its bf16 A tiles cost shared-memory round trips) wins
-    // for few large experts with >= 12 tokens each (Mixtral-shaped, T = 64: 0.48 ms against 0.61 ms).
-    const long long n_avg = (long long)f.n_tokens * c.top_k / std::max(1, c.num_experts);
-    const bool prefer_umma = n_avg >= 12 && c.hidden_size >= 4096;
-    if (f.tmaps2 && ffn_kind != B200MOE_FFN_GEMV && (ffn_kind == B200MOE_FFN_MMA || prefer_umma))
+    // The tcgen05 kernel (dequantised tiles in tensor memory) is faster than the register-fragment
+    // kernel at every measured batch (Mixtral-shaped T = 1..64, Qwen3-shaped T = 1..256); the latter
+    // stays reachable as B200MOE_FFN_GEMV and is what runs when no TMA descriptor could be made.
+    if (f.tmaps2 && ffn_kind != B200MOE_FFN_GEMV)
       return launch_ffn_int4_umma(ctx, p, f.tmaps2, st, f.max_n, f.n_tokens, s);
     return launch_ffn_int4(ctx, p, f.tmaps, st, f.max_n, s);
 #else
@@ -776,7 +774,14 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   FfnLaunch f{};
   f.experts = ctx->d_experts + (size_t)layer * E;
   f.offsets = ctx->offsets; f.sorted_pair = ctx->sorted_pair; f.act_list = ctx->act_list; f.n_act = ctx->n_act;
-  f.x = x; f.h = ctx->h; f.y = ctx->y; f.K = c.top_k; f.max_n = T;
+  f.x = x; f.h = ctx->h; f.y = ctx->y; f.K = c.top_k;
+  {
+    // Token-tile size: four times the mean load of an expert (measured best on uniform and on
+    // Zipf-skewed routing), at least 16, never more than the batch.  A popular expert that holds
+    // more tokens is processed in several passes over its weights, which then come from L2.
+    const long long n_mean = ((long long)T * c.top_k + E - 1) / E;
+    f.max_n = (int)std::min<long long>(T, std::max<long long>(16, 4 * n_mean));
+  }
   f.n_tokens = T;
   f.n_act_bound = (int)std::min<long long>(E, (long long)T * c.top_k);
   f.ksplit_ok = scores != nullptr;   // the expert-parallel scatter reads bf16 y

@@ -315,8 +315,9 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
       }
       for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
         int kb = first;
+        __nv_bfloat16 sv = sc[min(kb, nkb - 1)];
         for (; kb < nkb; kb += kI4uDeqGroups) {
-          const __nv_bfloat16 sv = sc[kb];
+          const __nv_bfloat16 sv_next = sc[min(kb + kI4uDeqGroups, nkb - 1)];   // the scale of this group's next stage is fetched a stage ahead
           if (!__all_sync(0xffffffffu, wait_or_abort(&w_full[ws], wph, abort_flag))) { ok = false; break; }   // warp-uniform
           const unsigned char* wrow = wrow0 + (size_t)ws * kI4uWTile;
           uint4 pk[4];
@@ -351,6 +352,7 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
           tc_fence_before();
           if (lane == 0) mbar_arrive(&full[grp]);
           ph ^= 1;
+          sv = sv_next;
         }
         first = kb - nkb;                         // the stride carries over into the next job
       }
