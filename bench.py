@@ -426,7 +426,8 @@ def run_ep(args, workload):
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if "RANK" in os.environ:
-        dist.init_process_group("nccl", device_id=dev)
+        import datetime
+        dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))   # a stuck collective is aborted, not waited for
     else:   # plain `python bench.py`: a one-rank group, no collectives are issued
         dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29555", rank=0, world_size=1, device_id=dev)
     batches = tuple(T for T in batches if T % world == 0)
@@ -462,7 +463,42 @@ def run_ep(args, workload):
         xl[T] = xs_full[T][sl.start:sl.stop].contiguous()
     from on_device_sd_b200.stack import MoEStack
     model = MoEStack(ctx, n_layers, ep)
-    one = (lambda T: model.forward(xl[T])) if stack else (lambda T: ep.forward(0, xl[T]))
+    eager = (lambda T: model.forward(xl[T])) if stack else (lambda T: ep.forward(0, xl[T]))
+    graphs = {}
+    launches_per_T = {}
+    for T in batches:                                  # kernels of this library one forward enqueues (a graph replay launches the same ones)
+        l_ = ctx.launches
+        eager(T)
+        launches_per_T[T] = ctx.launches - l_
+    if args.ep_graph:
+        # One CUDA graph per batch size: router, the NCCL collectives, permute, expert kernels and combine of
+        # every layer replay without a host launch in between (13 launches per layer when eager).
+        for T in batches:
+            for _ in range(2):
+                eager(T)
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        side = torch.cuda.Stream(device=dev)
+        dbg = os.environ.get("B200MOE_BENCH_DEBUG")
+        for T in batches:
+            if dbg: print(f"[rank {rank}] capturing T={T}", file=sys.stderr, flush=True)
+            g_ = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(g_, stream=side, capture_error_mode="thread_local"):
+                out_ = eager(T)
+            graphs[T] = (g_, out_)
+            if dbg: print(f"[rank {rank}] captured T={T}", file=sys.stderr, flush=True)
+        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
+        if dbg:
+            for T in batches:
+                graphs[T][0].replay(); torch.cuda.synchronize()
+                print(f"[rank {rank}] replayed T={T}", file=sys.stderr, flush=True)
+    if graphs and os.environ.get("B200MOE_BENCH_SYNC"):
+        def one(T):
+            graphs[T][0].replay(); torch.cuda.current_stream().synchronize()
+    else:
+        one = (lambda T: graphs[T][0].replay()) if graphs else eager
+    if os.environ.get("B200MOE_BENCH_DEBUG"):
+        import faulthandler
+        faulthandler.dump_traceback_later(45, exit=False, file=sys.stderr)
     def step():
         for T in batches:
             one(T)
@@ -470,7 +506,6 @@ def run_ep(args, workload):
         step()
     torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    l0 = ctx.launches
     e0.record()
     for _ in range(args.steps):
         step()
@@ -497,9 +532,9 @@ def run_ep(args, workload):
                           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                           "config": {"workload": workload, "layer": cfg_name, "hidden": H, "experts": E, "top_k": K, "intermediate": I,
                                      "token_batches": list(batches), "weights": wmode, "parallelism": f"ep{world}: {E // world} experts per GPU, "
-                                     "all-gather dispatch + sum reduce-scatter return over NCCL", "launch": "eager", "layers": n_layers,
+                                     "all-gather dispatch + sum reduce-scatter return over NCCL", "launch": "one CUDA graph replay per batch" if graphs else "eager", "layers": n_layers,
                                      "gate_bias": "zipf s=1.1 over a seeded permutation" if stack else None},
-                          "gpu_launches": ctx.launches - l0 - 20 * len(batches) * 0, "per_T": per_T}), flush=True)
+                          "gpu_launches": args.steps * sum(launches_per_T.values()), "per_T": per_T}), flush=True)
     dist.destroy_process_group()
 
 
@@ -514,12 +549,16 @@ def main():
     ap.add_argument("--batches", default=None, help="comma-separated token batches replacing the workload's sweep (profiling runs)")
     ap.add_argument("--ffn-kind", default="auto", choices=["auto", "gemv", "mma"], help="force one expert-FFN kernel family")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
+    ap.add_argument("--ep-graph", action="store_true", help="expert-parallel workloads: replay one CUDA graph per batch (with its NCCL collectives) instead of eager launches")
     ap.add_argument("--quick", action="store_true", help="timed region only: no e2e, per-T or CPU-baseline legs (for ncu captures)")
     args = ap.parse_args()
     if args.workload in EP_WORKLOADS:
         if args.impl == "reference":
             print(json.dumps({"impl": "reference", "unavailable": "the reference has no expert-parallel path (single GPU, demo/others.md:58-62)"}))
             return
+        if args.batches:
+            cfg, wm, _ = EP_WORKLOADS[args.workload]
+            EP_WORKLOADS[args.workload] = (cfg, wm, tuple(int(b) for b in args.batches.split(",")))
         return run_ep(args, args.workload)
     if args.batches:
         cfg, wm, _ = WORKLOADS[args.workload]

@@ -52,7 +52,7 @@ constexpr int kI4uACol0 = 256;            // first column of the A ring (accumul
 // Shared memory: the packed-tile ring (the bytes in flight from HBM) and a ring of token tiles.
 template <int NMAX> struct I4uShape {
   static constexpr int B_TILE = 2 * NMAX * 128;                 // two 64-k atoms of NMAX rows x 128 bytes
-  static constexpr int W_STAGES = NMAX <= 64 ? 12 : 8;          // 8 KB each; a multiple of the number of dequant groups
+  static constexpr int W_STAGES = NMAX <= 16 ? 20 : (NMAX == 32 ? 16 : (NMAX == 64 ? 12 : 8));   // 8 KB each; a multiple of the number of dequant groups
   static constexpr int A_STAGES = kI4uAStages;
   static constexpr int EX_BYTES = 64 * 17 * 4;
   static constexpr int FIXED = 1024 + W_STAGES * kI4uWTile + EX_BYTES + 512;

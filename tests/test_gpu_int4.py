@@ -112,3 +112,16 @@ def test_int4_mixtral_full_size_against_device_run_of_oracle():
     assert ctx.status() == 0
     want = O.moe_engine(L.x, ids, scores, deq, order=sorted(set(ids.flatten().tolist())))
     _close(out, want, L.dtype, tight=True)
+
+
+@pytest.mark.gpu
+def test_int4_popular_expert_exceeds_the_token_tile():
+    """As the bf16 case: tile of 16 rows, two experts with 64 tokens each -> four passes; I = 128 gives the
+    down projection a single k-stage, so the second MMA issuer never starts its accumulators."""
+    H, E, K, I, T = 256, 64, 2, 128, 64
+    L, ctx, deq = _int4_layer(H, E, K, I, T, seed=29)
+    ids = torch.tensor([[9, 5]] * T)
+    sc = torch.softmax(torch.randn(T, K, generator=torch.Generator().manual_seed(3)), -1).bfloat16()
+    out = ctx.forward(0, L.x.cuda(), ids.cuda(), sc.cuda())
+    assert ctx.status() == 0
+    _close(out, O.moe_engine(L.x, ids, sc, deq, order=[5, 9]), torch.bfloat16, tight=True)

@@ -270,3 +270,19 @@ def test_expert_ffn_tensor_core_path():
          "down_proj": (torch.randn(H, I, generator=g) * 0.02).bfloat16()}
     out = expert_forward_with_weights(x.cuda(), p["gate_proj"].cuda(), p["up_proj"].cuda(), p["down_proj"].cuda())
     _close(out, O.expert_ffn(x, **p), torch.bfloat16, tight=True)
+
+
+@pytest.mark.gpu
+def test_popular_expert_exceeds_the_token_tile():
+    """64 experts, every token picks the same two: the token tile is sized for the mean load (16 rows),
+    so the two popular experts take four passes each in the tensor-core kernel."""
+    from on_device_sd_b200.synth import make_layer
+    H, E, K, I, T = 256, 64, 2, 192, 64
+    L = make_layer(H, E, K, I, torch.bfloat16, T, seed=31)
+    ctx = _ctx(H, E, K, I, torch.bfloat16, max_tokens=64)
+    _register(ctx, L.experts)
+    ids = torch.tensor([[9, 5]] * T)
+    sc = torch.softmax(torch.randn(T, K, generator=torch.Generator().manual_seed(3)), -1).bfloat16()
+    out = ctx.forward(0, L.x.cuda(), ids.cuda(), sc.cuda())
+    assert ctx.status() == 0
+    _close(out, O.moe_engine(L.x, ids, sc, L.experts, order=[5, 9]), torch.bfloat16, tight=True)
