@@ -222,7 +222,7 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
   ctx->y = yb;
   ctx->scores = sb;
 #ifdef B200MOE_WITH_UMMA
-  if (cfg->act_dtype == B200MOE_BF16) {   // dense bf16 (tcgen05 path) and int4 (TMA boxes of packed nibbles)
+  if (cfg->act_dtype == B200MOE_BF16 || (cfg->act_dtype == B200MOE_F16 && cfg->weight_mode == B200MOE_W_DENSE)) {   // dense bf16 / fp16 (tcgen05 path) and int4 (TMA boxes of packed nibbles)
     ctx->h_tmaps.assign((L * E + 1) * 3, CUtensorMap{});
     ctx->tmap_ok.assign(L * E + 1, 0);
     if (cfg->weight_mode == B200MOE_W_INT4_G128) {
@@ -319,13 +319,13 @@ typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t,
                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
 // bf16 matrix [rows, cols] row-major -> 2-D tensor map with a {64 cols, box_rows} box, 128-byte swizzle
-static bool encode_map(b200moe_ctx* ctx, CUtensorMap* out, const void* base, int rows, int cols, int box_rows) {
+static bool encode_map(b200moe_ctx* ctx, CUtensorMap* out, const void* base, int rows, int cols, int box_rows, bool fp16 = false) {
   if (!ctx->encode_fn) return false;
   const cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
   const cuuint64_t strides[1] = {(cuuint64_t)cols * 2};
   const cuuint32_t box[2] = {64u, (cuuint32_t)box_rows};
   const cuuint32_t estr[2] = {1u, 1u};
-  CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_fn)(out, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
+  CUresult r = reinterpret_cast<EncodeTiledFn>(ctx->encode_fn)(out, fp16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box,
                                                                estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
                                                                CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS;
@@ -351,8 +351,9 @@ static bool encode_expert_maps(b200moe_ctx* ctx, CUtensorMap* three, const void*
     return encode_map_u8(ctx, &three[0], gate, I0, H0 / 2) && encode_map_u8(ctx, &three[1], up, I0, H0 / 2) &&
            encode_map_u8(ctx, &three[2], down, H0, I0 / 2);
   const int H = ctx->cfg.hidden_size, I = ctx->cfg.intermediate_size;
-  return encode_map(ctx, &three[0], gate, I, H, 64) && encode_map(ctx, &three[1], up, I, H, 64) &&
-         encode_map(ctx, &three[2], down, H, I, 128);
+  const bool fp16 = ctx->cfg.act_dtype == B200MOE_F16;
+  return encode_map(ctx, &three[0], gate, I, H, 64, fp16) && encode_map(ctx, &three[1], up, I, H, 64, fp16) &&
+         encode_map(ctx, &three[2], down, H, I, 128, fp16);
 }
 #endif
 
@@ -569,10 +570,10 @@ template <typename T, int NT> static int launch_gemv_pair(b200moe_ctx* ctx, cons
 }
 
 #ifdef B200MOE_WITH_UMMA
-template <int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, const UmmaParams& up, const SlotTable& st, cudaStream_t s) {
+template <typename T, int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, const UmmaParams& up, const SlotTable& st, cudaStream_t s) {
   using S = UmmaShape<NMAX>;
-  auto k_up = ffn_umma_kernel<NMAX, true>;
-  auto k_down = ffn_umma_kernel<NMAX, false>;
+  auto k_up = ffn_umma_kernel<T, NMAX, true>;
+  auto k_down = ffn_umma_kernel<T, NMAX, false>;
   static bool configured = false;
   if (!configured) {
     CUDA_TRY(ctx, cudaFuncSetAttribute(k_up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
@@ -613,10 +614,16 @@ static int launch_ffn_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tma
     up.ksplit = std::max(1, ks);
   }
   ctx->last_ksplit = up.ksplit;
-  if (max_n <= 16) return launch_umma_pair<16>(ctx, up, st, s);
-  if (max_n <= 32) return launch_umma_pair<32>(ctx, up, st, s);
-  if (max_n <= 64) return launch_umma_pair<64>(ctx, up, st, s);
-  return launch_umma_pair<128>(ctx, up, st, s);
+  if (ctx->cfg.act_dtype == B200MOE_F16) {
+    if (max_n <= 16) return launch_umma_pair<__half, 16>(ctx, up, st, s);
+    if (max_n <= 32) return launch_umma_pair<__half, 32>(ctx, up, st, s);
+    if (max_n <= 64) return launch_umma_pair<__half, 64>(ctx, up, st, s);
+    return launch_umma_pair<__half, 128>(ctx, up, st, s);
+  }
+  if (max_n <= 16) return launch_umma_pair<__nv_bfloat16, 16>(ctx, up, st, s);
+  if (max_n <= 32) return launch_umma_pair<__nv_bfloat16, 32>(ctx, up, st, s);
+  if (max_n <= 64) return launch_umma_pair<__nv_bfloat16, 64>(ctx, up, st, s);
+  return launch_umma_pair<__nv_bfloat16, 128>(ctx, up, st, s);
 }
 #endif
 
@@ -723,7 +730,7 @@ static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st,
 #endif
   }
 #ifdef B200MOE_WITH_UMMA
-  if (c.act_dtype == B200MOE_BF16 && ffn_kind != B200MOE_FFN_GEMV && (ffn_kind == B200MOE_FFN_MMA || f.max_n > 1)) {
+  if ((c.act_dtype == B200MOE_BF16 || c.act_dtype == B200MOE_F16) && ffn_kind != B200MOE_FFN_GEMV && (ffn_kind == B200MOE_FFN_MMA || f.max_n > 1)) {
     int rc = launch_ffn_umma(ctx, p, f.tmaps, st, f.max_n, f.n_act_bound, f.ksplit_ok, s);
     if (rc != B200MOE_E_UNSUPPORTED) return rc;
     if (ffn_kind == B200MOE_FFN_MMA) return rc;

@@ -129,6 +129,11 @@ __device__ __forceinline__ uint64_t umma_desc_sw128(uint32_t saddr) {
 __device__ __forceinline__ uint32_t umma_idesc_bf16(int n) {
   return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
 }
+// the same with the operand format of the model dtype: 0 = fp16, 1 = bf16 (bits 7-9 for A, 10-12 for B)
+template <typename T> __device__ __forceinline__ uint32_t umma_idesc(int n) {
+  constexpr uint32_t fmt = std::is_same<T, __half>::value ? 0u : 1u;
+  return (1u << 4) | (fmt << 7) | (fmt << 10) | ((uint32_t)(n >> 3) << 17) | ((128u >> 4) << 24);
+}
 
 // Bounded wait that also leaves when another role has raised the CTA's abort flag.  The first
 // probe costs one instruction; after that the warp sleeps between probes - a spinning warp takes
@@ -148,8 +153,9 @@ __device__ __forceinline__ bool wait_or_abort(uint64_t* bar, uint32_t parity, vo
   }
 }
 
-template <int NMAX, bool DUAL>
+template <typename T, int NMAX, bool DUAL>
 __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up, SlotTable st) {
+  static_assert(std::is_same<T, __nv_bfloat16>::value || std::is_same<T, __half>::value, "16-bit model dtypes only");
   using S = UmmaShape<NMAX>;
   constexpr int STAGES = S::STAGES;
   constexpr int B_TILE = S::B_TILE;
@@ -162,7 +168,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   unsigned char* As = smem;
   unsigned char* Bs = smem + (size_t)STAGES * kUmmaATile;
   float* ex = reinterpret_cast<float*>(Bs + (size_t)STAGES * B_TILE);
-  const __nv_bfloat16** rowptr = reinterpret_cast<const __nv_bfloat16**>(reinterpret_cast<unsigned char*>(ex) + S::EX_BYTES);
+  const T** rowptr = reinterpret_cast<const T**>(reinterpret_cast<unsigned char*>(ex) + S::EX_BYTES);
   uint64_t* full = reinterpret_cast<uint64_t*>(reinterpret_cast<unsigned char*>(rowptr) + S::PTR_BYTES);
   uint64_t* empty = full + STAGES;
   uint64_t* acc_full = empty + STAGES;
@@ -249,7 +255,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
       const int n = warp_bcast(p.offsets[e + 1] - p.offsets[e]);
       for (int c0 = 0; c0 < n && ok; c0 += NMAX, ++job) {
         const int npad = (min(NMAX, n - c0) + 15) & ~15;
-        const uint32_t idesc = umma_idesc_bf16(npad);
+        const uint32_t idesc = umma_idesc<T>(npad);
         const int b = job & 1;
         if (!__all_sync(0xffffffffu, wait_or_abort(&acc_empty[b], ((job >> 1) & 1) ^ 1, abort_flag))) { ok = false; break; }
         tc_fence_after();
@@ -287,8 +293,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
         asm volatile("bar.sync 2, 128;" ::: "memory");
         if (tl < npad) {
           const int pos = pos0 + c0 + min(tl, nt - 1);
-          rowptr[tl] = DUAL ? reinterpret_cast<const __nv_bfloat16*>(p.x) + (size_t)(p.sorted_pair[pos] / p.K) * p.H
-                            : reinterpret_cast<const __nv_bfloat16*>(p.h) + (size_t)pos * p.I;
+          rowptr[tl] = DUAL ? reinterpret_cast<const T*>(p.x) + (size_t)(p.sorted_pair[pos] / p.K) * p.H
+                            : reinterpret_cast<const T*>(p.h) + (size_t)pos * p.I;
         }
         asm volatile("bar.sync 2, 128;" ::: "memory");
         for (int kb = kb0; kb < kb1 && ok; ++kb) {
@@ -298,7 +304,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
             const int r = id >> 3, chunk = id & 7;
             const int k0 = kb * kUmmaBK + chunk * 8;
             const bool live = (r < nt) && (k0 < Kdim);
-            const __nv_bfloat16* src = rowptr[r];
+            const T* src = rowptr[r];
             cp_async_16(bt + r * 128 + ((chunk ^ (r & 7)) << 4), live ? (const void*)(src + k0) : (const void*)src, live ? 16u : 0u);
           }
           cp_async_commit();
@@ -328,8 +334,8 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
     const int et = threadIdx.x - 192;             // 0..127
     int job = 0;
     bool ok = true;
-    __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h);
-    __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(p.y);
+    T* hout = reinterpret_cast<T*>(p.h);
+    T* yout = reinterpret_cast<T*>(p.y);
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
       B200MOE_DECODE_ITEM(item)
       const int pos0 = p.offsets[e];
@@ -360,7 +366,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
             if (q >= 2) {
               const int row = (q - 2) * 32 + lane;
 #pragma unroll
-              for (int j = 0; j < 16; ++j) ex[row * 17 + j] = rn<__nv_bfloat16>(__uint_as_float(r[j]));
+              for (int j = 0; j < 16; ++j) ex[row * 17 + j] = rn<T>(__uint_as_float(r[j]));
             }
             asm volatile("bar.sync 1, 128;" ::: "memory");
             if (q < 2) {
@@ -369,10 +375,10 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
 #pragma unroll
               for (int j = 0; j < 16; ++j) {
                 if (col + j < nt && grow < Rdim) {
-                  const float g = rn<__nv_bfloat16>(__uint_as_float(r[j]));
+                  const float g = rn<T>(__uint_as_float(r[j]));
                   const float u = ex[row * 17 + j];
-                  const float sg = rn<__nv_bfloat16>(silu_f32(g));
-                  hout[(size_t)(pos0 + c0 + col + j) * p.I + grow] = __float2bfloat16_rn(__fmul_rn(sg, u));
+                  const float sg = rn<T>(silu_f32(g));
+                  hout[(size_t)(pos0 + c0 + col + j) * p.I + grow] = Elem<T>::from_float(__fmul_rn(sg, u));
                 }
               }
             }
@@ -383,7 +389,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
             for (int j = 0; j < 16; ++j)
               if (col + j < nt && grow < Rdim) {
                 if (KS > 1) up.ypart[((size_t)ks_ * up.pairs_cap + (pos0 + c0 + col + j)) * p.H + grow] = __uint_as_float(r[j]);
-                else yout[(size_t)(pos0 + c0 + col + j) * p.H + grow] = __float2bfloat16_rn(__uint_as_float(r[j]));
+                else yout[(size_t)(pos0 + c0 + col + j) * p.H + grow] = Elem<T>::from_float(__uint_as_float(r[j]));
               }
           }
         }

@@ -230,35 +230,38 @@ def _kinds():
     return {"gemv": FFN_GEMV, "mma": FFN_MMA}
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("kind", ["gemv", "mma"])
 @pytest.mark.parametrize("T", [1, 3, 16, 17, 40])
-def test_kernel_families_small_bf16(kind, T):
+def test_kernel_families_small_16bit(kind, T, dtype):
+    """Both 16-bit model dtypes (the reference's default is float16, demo/src/core/model.py:122-129)."""
     from on_device_sd_b200.synth import make_layer
     H, E, K, I = 256, 16, 4, 192          # I is not a multiple of the 64-row tile of the tensor-core kernel
-    L = make_layer(H, E, K, I, torch.bfloat16, T, seed=11)
-    ctx = _ctx(H, E, K, I, torch.bfloat16, max_tokens=64)
+    L = make_layer(H, E, K, I, dtype, T, seed=11)
+    ctx = _ctx(H, E, K, I, dtype, max_tokens=64)
     ctx.set_gate(0, L.gate_w.cuda())
     _register(ctx, L.experts)
     out, ids, scores = ctx.forward_fused(0, L.x.cuda(), return_routing=True, ffn_kind=_kinds()[kind])
     assert ctx.status() == 0
     want = O.moe_engine(L.x, ids.cpu(), scores.cpu(), L.experts, order=sorted(set(ids.flatten().tolist())))
-    _close(out, want, torch.bfloat16, tight=True)
+    _close(out, want, dtype, tight=True)
 
 
 @pytest.mark.parametrize("kind", ["gemv", "mma"])
-def test_kernel_families_many_tokens_one_expert(kind):
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_kernel_families_many_tokens_one_expert(kind, dtype):
     """200 tokens all routed to the same two experts: more than one pass of 128 tokens in the
     tensor-core kernel, 50 passes of 4 in the GEMV kernel; K = 328 is not a multiple of 64."""
     from on_device_sd_b200.synth import make_layer
     H, E, K, I, T = 328, 4, 2, 136, 200
-    L = make_layer(H, E, K, I, torch.bfloat16, T, seed=12)
-    ctx = _ctx(H, E, K, I, torch.bfloat16, max_tokens=256)
+    L = make_layer(H, E, K, I, dtype, T, seed=12)
+    ctx = _ctx(H, E, K, I, dtype, max_tokens=256)
     _register(ctx, L.experts)
     ids = torch.tensor([[3, 1]] * T)
-    sc = torch.softmax(torch.randn(T, K, generator=torch.Generator().manual_seed(2)), -1).bfloat16()
+    sc = torch.softmax(torch.randn(T, K, generator=torch.Generator().manual_seed(2)), -1).to(dtype)
     out = ctx.forward(0, L.x.cuda(), ids.cuda(), sc.cuda(), ffn_kind=_kinds()[kind])
     assert ctx.status() == 0
-    _close(out, O.moe_engine(L.x, ids, sc, L.experts, order=[1, 3]), torch.bfloat16, tight=True)
+    _close(out, O.moe_engine(L.x, ids, sc, L.experts, order=[1, 3]), dtype, tight=True)
 
 
 def test_expert_ffn_tensor_core_path():
