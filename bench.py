@@ -535,6 +535,15 @@ def run_ep(args, workload):
                                      "all-gather dispatch + sum reduce-scatter return over NCCL", "launch": "one CUDA graph replay per batch" if graphs else "eager", "layers": n_layers,
                                      "gate_bias": "zipf s=1.1 over a seeded permutation" if stack else None},
                           "gpu_launches": args.steps * sum(launches_per_T.values()), "per_T": per_T}), flush=True)
+    if graphs:
+        # Tearing the process group down while captured graphs still hold its collectives blocks forever
+        # (observed: the line above was printed, destroy_process_group never returned): drop the graphs, then leave.
+        for g_, _ in graphs.values():
+            g_.reset()
+        graphs.clear()
+        torch.cuda.synchronize()
+        sys.stdout.flush(); sys.stderr.flush()
+        os._exit(0)
     dist.destroy_process_group()
 
 
