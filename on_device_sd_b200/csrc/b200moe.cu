@@ -536,7 +536,8 @@ struct FfnLaunch {
 
 using GemvDefault = GemvShape<8, 2048, 3>;
 
-template <typename T, int NT, typename S> static int launch_gemv_pair_shape(b200moe_ctx* ctx, const FfnParams& p, const SlotTable& st, cudaStream_t s) {
+// which: bit 0 = gate/up projection, bit 1 = down projection
+template <typename T, int NT, typename S> static int launch_gemv_pair_shape(b200moe_ctx* ctx, const FfnParams& p, const SlotTable& st, cudaStream_t s, int which = 3) {
   const int grid = ctx->sm_count;   // one persistent CTA per SM: the rings take most of its shared memory
   auto up = ffn_gemv_kernel<T, NT, true, S>;
   auto down = ffn_gemv_kernel<T, NT, false, S>;
@@ -546,12 +547,15 @@ template <typename T, int NT, typename S> static int launch_gemv_pair_shape(b200
     CUDA_TRY(ctx, cudaFuncSetAttribute(down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
     configured = true;
   }
-  {
-    ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
-    launch_chain(up, dim3(grid), dim3(S::THREADS), S::SMEM, s, p, st, ctx->status);
+  if (which & 1) {
+    {
+      ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
+      launch_chain(up, dim3(grid), dim3(S::THREADS), S::SMEM, s, p, st, ctx->status);
+    }
+    int rc = post_launch(ctx, "ffn_gemv_kernel<gate/up>");
+    if (rc) return rc;
   }
-  int rc = post_launch(ctx, "ffn_gemv_kernel<gate/up>");
-  if (rc) return rc;
+  if (!(which & 2)) return B200MOE_OK;
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_DOWN, s);
     launch_chain(down, dim3(grid), dim3(S::THREADS), S::SMEM, s, p, st, ctx->status);
@@ -559,18 +563,18 @@ template <typename T, int NT, typename S> static int launch_gemv_pair_shape(b200
   return post_launch(ctx, "ffn_gemv_kernel<down>");
 }
 
-template <typename T, int NT> static int launch_gemv_pair(b200moe_ctx* ctx, const FfnParams& p, const SlotTable& st, cudaStream_t s) {
+template <typename T, int NT> static int launch_gemv_pair(b200moe_ctx* ctx, const FfnParams& p, const SlotTable& st, cudaStream_t s, int which = 3) {
   switch (ctx->gemv_variant) {   // tuning knob (environment variable B200MOE_GEMV_VARIANT at create time)
-    case 1: return launch_gemv_pair_shape<T, NT, GemvShape<16, 1024, 3>>(ctx, p, st, s);
-    case 2: return launch_gemv_pair_shape<T, NT, GemvShape<8, 1024, 6>>(ctx, p, st, s);
-    case 3: return launch_gemv_pair_shape<T, NT, GemvShape<8, 4096, 2>>(ctx, p, st, s);
-    case 4: return launch_gemv_pair_shape<T, NT, GemvShape<16, 2048, 2>>(ctx, p, st, s);
-    default: return launch_gemv_pair_shape<T, NT, GemvDefault>(ctx, p, st, s);
+    case 1: return launch_gemv_pair_shape<T, NT, GemvShape<16, 1024, 3>>(ctx, p, st, s, which);
+    case 2: return launch_gemv_pair_shape<T, NT, GemvShape<8, 1024, 6>>(ctx, p, st, s, which);
+    case 3: return launch_gemv_pair_shape<T, NT, GemvShape<8, 4096, 2>>(ctx, p, st, s, which);
+    case 4: return launch_gemv_pair_shape<T, NT, GemvShape<16, 2048, 2>>(ctx, p, st, s, which);
+    default: return launch_gemv_pair_shape<T, NT, GemvDefault>(ctx, p, st, s, which);
   }
 }
 
 #ifdef B200MOE_WITH_UMMA
-template <typename T, int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, const UmmaParams& up, const SlotTable& st, cudaStream_t s) {
+template <typename T, int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, const UmmaParams& up, const SlotTable& st, cudaStream_t s, int which = 3) {
   using S = UmmaShape<NMAX>;
   auto k_up = ffn_umma_kernel<T, NMAX, true>;
   auto k_down = ffn_umma_kernel<T, NMAX, false>;
@@ -580,12 +584,15 @@ template <typename T, int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, co
     CUDA_TRY(ctx, cudaFuncSetAttribute(k_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
     configured = true;
   }
-  {
-    ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
-    launch_chain(k_up, dim3(ctx->sm_count), dim3(kUmmaThreads), S::SMEM, s, up, st);
+  if (which & 1) {
+    {
+      ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
+      launch_chain(k_up, dim3(ctx->sm_count), dim3(kUmmaThreads), S::SMEM, s, up, st);
+    }
+    int rc = post_launch(ctx, "ffn_umma_kernel<gate/up>");
+    if (rc) return rc;
   }
-  int rc = post_launch(ctx, "ffn_umma_kernel<gate/up>");
-  if (rc) return rc;
+  if (!(which & 2)) return B200MOE_OK;
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_DOWN, s);
     launch_chain(k_down, dim3(ctx->sm_count), dim3(kUmmaThreads), S::SMEM, s, up, st);
@@ -596,7 +603,7 @@ template <typename T, int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, co
 // max_n bounds the tokens any expert can hold in this call (the batch size); a pass of the
 // kernel covers NMAX tokens, so larger per-expert counts only cost extra passes.
 static int launch_ffn_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tmaps, const SlotTable& st, int max_n, int n_act_bound,
-                           bool ksplit_ok, cudaStream_t s) {
+                           bool ksplit_ok, cudaStream_t s, int which = 3) {
   if (!tmaps) return fail(ctx, B200MOE_E_UNSUPPORTED, "tensor-core path unavailable: no TMA descriptors for these experts");
   UmmaParams up{};
   up.f = p;
@@ -615,15 +622,15 @@ static int launch_ffn_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tma
   }
   ctx->last_ksplit = up.ksplit;
   if (ctx->cfg.act_dtype == B200MOE_F16) {
-    if (max_n <= 16) return launch_umma_pair<__half, 16>(ctx, up, st, s);
-    if (max_n <= 32) return launch_umma_pair<__half, 32>(ctx, up, st, s);
-    if (max_n <= 64) return launch_umma_pair<__half, 64>(ctx, up, st, s);
-    return launch_umma_pair<__half, 128>(ctx, up, st, s);
+    if (max_n <= 16) return launch_umma_pair<__half, 16>(ctx, up, st, s, which);
+    if (max_n <= 32) return launch_umma_pair<__half, 32>(ctx, up, st, s, which);
+    if (max_n <= 64) return launch_umma_pair<__half, 64>(ctx, up, st, s, which);
+    return launch_umma_pair<__half, 128>(ctx, up, st, s, which);
   }
-  if (max_n <= 16) return launch_umma_pair<__nv_bfloat16, 16>(ctx, up, st, s);
-  if (max_n <= 32) return launch_umma_pair<__nv_bfloat16, 32>(ctx, up, st, s);
-  if (max_n <= 64) return launch_umma_pair<__nv_bfloat16, 64>(ctx, up, st, s);
-  return launch_umma_pair<__nv_bfloat16, 128>(ctx, up, st, s);
+  if (max_n <= 16) return launch_umma_pair<__nv_bfloat16, 16>(ctx, up, st, s, which);
+  if (max_n <= 32) return launch_umma_pair<__nv_bfloat16, 32>(ctx, up, st, s, which);
+  if (max_n <= 64) return launch_umma_pair<__nv_bfloat16, 64>(ctx, up, st, s, which);
+  return launch_umma_pair<__nv_bfloat16, 128>(ctx, up, st, s, which);
 }
 #endif
 
@@ -730,6 +737,17 @@ static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st,
 #endif
   }
 #ifdef B200MOE_WITH_UMMA
+  if ((c.act_dtype == B200MOE_BF16 || c.act_dtype == B200MOE_F16) && ffn_kind == B200MOE_FFN_AUTO && f.max_n <= 1 && f.tmaps) {
+    // Single token: the GEMV kernel is the faster gate/up projection (2 rows per warp unit fill the GPU),
+    // the tensor-core kernel with its K split the faster down projection (measured 47 against 65 us on the
+    // Mixtral-shaped layer, 13 against 16.5 us on the Qwen3-shaped one).  Both use the same h layout.
+    int rc = dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
+      using T = decltype(tag);
+      return launch_gemv_pair<T, 1>(ctx, p, st, s, 1);
+    });
+    if (rc) return rc;
+    return launch_ffn_umma(ctx, p, f.tmaps, st, f.max_n, f.n_act_bound, f.ksplit_ok, s, 2);
+  }
   if ((c.act_dtype == B200MOE_BF16 || c.act_dtype == B200MOE_F16) && ffn_kind != B200MOE_FFN_GEMV && (ffn_kind == B200MOE_FFN_MMA || f.max_n > 1)) {
     int rc = launch_ffn_umma(ctx, p, f.tmaps, st, f.max_n, f.n_act_bound, f.ksplit_ok, s);
     if (rc != B200MOE_E_UNSUPPORTED) return rc;
