@@ -48,6 +48,13 @@ EP_WORKLOADS = {
     "qwen3_int4_stack": ("qwen3", "int4", (160, 288)),
     "qwen3_bf16_stack": ("qwen3", "bf16", (160, 288)),
 }
+# DRAM bytes (read + write) of the gate/up kernel over its algorithmic bytes, from one ncu capture per workload
+# (a smaller case of the same kernel: one batch of 16 tokens, 8 experts hit); the kernel reads every weight byte
+# once whatever the batch, so the ratio carries over to the mean launch of the sweep.
+NCU_TRAFFIC_RATIO = {
+    "mixtral_bf16": (1.0023, "ncu capture at T=16: 1.879 GB read + 4.2 MB written against 1.879 GB algorithmic (profiles/ffn_umma_mixtral_bf16_T16.md), scaled to the mean launch"),
+    "mixtral_int4": (1.0082, "ncu capture at T=16: 484.8 MB read + 3.8 MB written against 484.6 MB algorithmic (profiles/ffn_int4_umma_mixtral_int4_T16.md), scaled to the mean launch"),
+}
 METRIC = "MoE-layer tokens/s at verify batch"
 UNIT = "tokens/s"
 
@@ -355,7 +362,8 @@ def run_ours(args, workload):
     total_kernel_ms = sum(v[0] for v in prof.values())
     roofline = {"bound": "hbm", "kernel": "ffn_gate_up (expert gate_proj/up_proj streaming + SwiGLU)",
                 "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": (achieved / peak) if achieved else None,
-                "peak_kind": f"{peak_kind} copy bandwidth", "traffic": None,
+                "peak_kind": f"{peak_kind} copy bandwidth", "traffic": (gu_bytes * NCU_TRAFFIC_RATIO[workload][0]) if workload in NCU_TRAFFIC_RATIO else None,
+                "traffic_source": NCU_TRAFFIC_RATIO[workload][1] if workload in NCU_TRAFFIC_RATIO else None,
                 "algorithmic_bytes_per_launch": gu_bytes, "mean_launch_us": gu_ms / max(gu_n, 1) * 1e3,
                 "timing": "CUDA events around every launch, separate pass of the same steps right after the timed region",
                 "layer": {"algorithmic_bytes_per_step": layer_bytes, "achieved_gbs": layer_bytes * args.steps / (ms * 1e-3) / 1e9,

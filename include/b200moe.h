@@ -165,6 +165,15 @@ int b200moe_ep_combine(b200moe_ctx* ctx, const void* y_pairs, int T, const int64
 int b200moe_expert_ffn(b200moe_ctx* ctx, const void* x, int n, const void* gate_proj, const void* up_proj,
                        const void* down_proj, void* out, void* stream);
 
+/* RMSNorm in front of the MoE block, optionally fused with the residual add before it
+ * (RMSNorm.rms_forward / add_rms_forward, demo/src/layers/layernorm.py:21-36; the call site is
+ * `layer.post_attention_layernorm`, demo/src/model/qwen3_runner.py:204).
+ *   s = float(x) [+ float(residual)];  residual_out = T(s);  out = T( T(s * rsqrt(mean(s^2) + eps)) * weight )
+ *   x, residual, out, residual_out [T,H] and weight [H] in the context's activation dtype, H = hidden_size.
+ *   residual_out is written only when residual is given; out may alias x, residual_out may alias residual. */
+int b200moe_rmsnorm(b200moe_ctx* ctx, const void* x, const void* residual_or_null, const void* weight, float eps, int T,
+                    void* out, void* residual_out_or_null, void* stream);
+
 /* The same FFN for callers that cannot allocate device memory.  It has no counterpart in the
  * reference.  b200moe_expert_ffn needs a context, and creating one allocates its workspace; an
  * engine that has already handed the whole GPU to its own pools, or code running inside a section

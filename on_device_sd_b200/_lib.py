@@ -7,7 +7,7 @@ from __future__ import annotations
 
 import ctypes
 import os
-from ctypes import POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_void_p
+from ctypes import c_float, POINTER, Structure, c_char_p, c_int, c_int32, c_int64, c_void_p
 from pathlib import Path
 
 PKG = Path(__file__).resolve().parent
@@ -49,6 +49,7 @@ PROTOTYPES = {
     "b200moe_ep_local_experts": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_ep_combine": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, POINTER(c_int32), c_void_p, c_void_p, c_void_p]),
     "b200moe_expert_ffn": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200moe_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_expert_ffn_noalloc": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_pack_int4": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_unpack_int4": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),

@@ -231,6 +231,19 @@ class MoEContext:
                                                  _ptr(out), _stream(self.device)))
         return out
 
+    def rmsnorm(self, x2d: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None):
+        """RMSNorm of [T,H] rows, optionally fused with the residual add in front of it
+        (demo/src/layers/layernorm.py:21-36).  Returns `out`, or `(out, new_residual)` when `residual` is given."""
+        _need_cuda(x2d, "x", self.device, self.dtype)
+        _need_cuda(weight, "weight", self.device, self.dtype)
+        if residual is not None:
+            _need_cuda(residual, "residual", self.device, self.dtype)
+        out = torch.empty_like(x2d)
+        res_out = torch.empty_like(x2d) if residual is not None else None
+        self._check(self._lib.b200moe_rmsnorm(self._h, _ptr(x2d), _ptr(residual), _ptr(weight), float(eps), x2d.shape[0],
+                                              _ptr(out), _ptr(res_out), _stream(self.device)))
+        return out if residual is None else (out, res_out)
+
     def profile(self, enable: bool) -> None:
         """Turns per-kernel CUDA-event timing on or off (benchmarks only)."""
         self._check(self._lib.b200moe_profile(self._h, 1 if enable else 0))

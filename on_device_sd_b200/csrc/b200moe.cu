@@ -20,6 +20,7 @@
 #include "ffn_gemv.cuh"
 #include "int4_pack.cuh"
 #include "permute.cuh"
+#include "rmsnorm.cuh"
 #include "router.cuh"
 #ifdef B200MOE_WITH_INT4
 #include "ffn_int4.cuh"
@@ -935,6 +936,31 @@ extern "C" int b200moe_ep_combine(b200moe_ctx* ctx, const void* y_pairs, int T, 
     ProfScope prof(ctx, B200MOE_KERNEL_COMBINE, st);
     launch_chain(combine_kernel<Tt>, dim3(T), dim3(kCombineThreads), 0, st, cp, tab);
     return post_launch(ctx, "combine_kernel");
+  });
+}
+
+extern "C" int b200moe_rmsnorm(b200moe_ctx* ctx, const void* x, const void* residual_or_null, const void* weight, float eps, int T,
+                               void* out, void* residual_out_or_null, void* stream) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_rmsnorm: null context");
+  const b200moe_config& c = ctx->cfg;
+  if (T < 0) return fail(ctx, B200MOE_E_ARG, "b200moe_rmsnorm: negative row count");
+  if (T == 0) return B200MOE_OK;
+  if (!x || !weight || !out) return fail(ctx, B200MOE_E_ARG, "b200moe_rmsnorm: null pointer");
+  if (misaligned(x) || misaligned(weight) || misaligned(out) || (residual_or_null && misaligned(residual_or_null)) ||
+      (residual_out_or_null && misaligned(residual_out_or_null)))
+    return fail(ctx, B200MOE_E_ARG, "b200moe_rmsnorm: pointers must be 16-byte aligned");
+  if (c.hidden_size % 8 || c.hidden_size > kNormThreads * kNormMaxChunks * 8)
+    return fail(ctx, B200MOE_E_UNSUPPORTED, "b200moe_rmsnorm: hidden size %d (multiples of 8 up to %d)", c.hidden_size, kNormThreads * kNormMaxChunks * 8);
+  CUDA_TRY(ctx, cudaSetDevice(c.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  NormParams p{};
+  p.x = x; p.residual = residual_or_null; p.weight = weight; p.out = out;
+  p.residual_out = residual_or_null ? residual_out_or_null : nullptr;
+  p.eps = eps; p.T = T; p.H = c.hidden_size;
+  return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
+    using Tt = decltype(tag);
+    launch_chain(rmsnorm_kernel<Tt>, dim3(T), dim3(kNormThreads), 0, st, p);
+    return post_launch(ctx, "rmsnorm_kernel");
   });
 }
 

@@ -1,5 +1,5 @@
 """Module-level drop-ins with the reference's layer signatures
-(demo/src/layers/moe_layer.py:14-254, demo/src/layers/mlp.py:209-231)."""
+(demo/src/layers/moe_layer.py:14-254, demo/src/layers/mlp.py:209-231, demo/src/layers/layernorm.py:9-47)."""
 from __future__ import annotations
 
 from typing import Dict, Optional, Tuple
@@ -108,3 +108,29 @@ class Qwen3MoELayer(Qwen3MoELayerWithWeights):
 
     def forward(self, hidden_states: torch.Tensor, expert_weights_dict) -> torch.Tensor:  # type: ignore[override]
         return self._run(hidden_states, self.gate.gate.weight, expert_weights_dict)
+
+
+class RMSNorm(nn.Module):
+    """The reference's RMSNorm (demo/src/layers/layernorm.py:9-47) with both forms in one kernel launch:
+    `forward(x)` -> normed, `forward(x, residual)` -> (normed, x + residual).  The weight is used in the
+    activation dtype, as it is once the reference has cast the model to its dtype."""
+
+    def __init__(self, hidden_size: int, eps: float = 1e-6) -> None:
+        super().__init__()
+        self.eps = eps
+        self.weight = nn.Parameter(torch.ones(hidden_size))
+
+    def forward(self, x: torch.Tensor, residual: Optional[torch.Tensor] = None):
+        H = x.shape[-1]
+        flat = x.reshape(-1, H).contiguous()
+        n = flat.shape[0]
+        key = (x.device.index, x.dtype, H, 0)
+        ctx = _FFN_CTX.get(key)
+        if ctx is None:
+            ctx = MoEContext(H, 1, 1, 8, x.dtype, num_layers=1, max_tokens=8, weight_mode=W_DENSE, device=x.device)
+            _FFN_CTX[key] = ctx
+        w = self.weight.detach().to(device=x.device, dtype=x.dtype).contiguous()
+        if residual is None:
+            return ctx.rmsnorm(flat, w, self.eps).view(x.shape)
+        out, res = ctx.rmsnorm(flat, w, self.eps, residual.reshape(-1, H).contiguous())
+        return out.view(x.shape), res.view(x.shape)

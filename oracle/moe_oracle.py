@@ -231,6 +231,17 @@ def layer_activations(ids: torch.Tensor, scores: torch.Tensor, num_experts: int)
     return out
 
 
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, residual: Optional[torch.Tensor] = None):
+    """RMSNorm.rms_forward / add_rms_forward (demo/src/layers/layernorm.py:21-36): fp32 statistics, the
+    normalised row rounded to the input dtype, then multiplied by the weight.  Returns out, or
+    (out, new_residual) when `residual` is given."""
+    orig = x.dtype
+    s = x.float() if residual is None else x.float() + residual.float()
+    var = s.pow(2).mean(dim=-1, keepdim=True)
+    out = (s * torch.rsqrt(var + eps)).to(orig) * weight
+    return out if residual is None else (out, s.to(orig))
+
+
 # --------------------------------------------------------------------------------------
 # expert FFN and the two MoE block paths
 # --------------------------------------------------------------------------------------

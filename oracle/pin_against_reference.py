@@ -177,6 +177,28 @@ def main() -> None:
                         tokens=torch.cat([m[2] for m in mine]).numpy(), act_scores=to_np(torch.cat([m[3] for m in mine])))
     print(f"activations_bf16: {len(mine)} activations == reference")
 
+    # RMSNorm in front of the MoE block (demo/src/layers/layernorm.py:9-47), both forms, weight in the model dtype
+    from src.layers.layernorm import RMSNorm
+    g = torch.Generator().manual_seed(9)
+    rec = {}
+    for name, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
+        x = torch.randn(12, 256, generator=g).to(dt)
+        r = torch.randn(12, 256, generator=g).to(dt)
+        w = (1.0 + 0.1 * torch.randn(256, generator=g)).to(dt)
+        m = RMSNorm(256, eps=1e-6)
+        with torch.no_grad():
+            m.weight.copy_(w.float())
+            m = m.to(dt)
+            ref1 = m(x)
+            ref2, ref_res = m(x, r)
+            o1 = O.rmsnorm(x, w, 1e-6)
+            o2, ores = O.rmsnorm(x, w, 1e-6, r)
+        assert ref1.dtype == dt and torch.equal(ref1, o1) and torch.equal(ref2, o2) and torch.equal(ref_res, ores), name
+        rec.update({f"{name}_x": to_np(x), f"{name}_r": to_np(r), f"{name}_w": to_np(w), f"{name}_out": to_np(ref1),
+                    f"{name}_out_add": to_np(ref2), f"{name}_res": to_np(ref_res)})
+    np.savez_compressed(golden / "rmsnorm.npz", **rec)
+    print("rmsnorm: restatement == reference bit for bit (bf16, f16, f32; with and without residual)")
+
     # int4 g128: the format is this build's; store a small packed example produced by the oracle
     g = torch.Generator().manual_seed(7)
     w = (torch.randn(24, 384, generator=g) * 0.02).to(torch.bfloat16)

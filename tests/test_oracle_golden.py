@@ -112,3 +112,13 @@ def test_route_shapes_and_edge_cases(T, E, K):
         assert bool((ids.sort(-1).values == torch.topk(logits, K).indices.sort(-1).values).all())
         for t in range(T):
             assert len(set(ids[t].tolist())) == K
+
+
+def test_rmsnorm_restatement_matches_reference_fixture():
+    """tests/golden/rmsnorm.npz holds outputs of the reference's RMSNorm (demo/src/layers/layernorm.py:9-47)."""
+    z = np.load(GOLDEN / "rmsnorm.npz")
+    for name, dt in (("bf16", torch.bfloat16), ("f16", torch.float16), ("f32", torch.float32)):
+        x, r, w = (from_np(z[f"{name}_{k}"], dt) for k in ("x", "r", "w"))
+        assert torch.equal(O.rmsnorm(x, w, 1e-6), from_np(z[f"{name}_out"], dt))
+        out, res = O.rmsnorm(x, w, 1e-6, r)
+        assert torch.equal(out, from_np(z[f"{name}_out_add"], dt)) and torch.equal(res, from_np(z[f"{name}_res"], dt))
