@@ -7,13 +7,14 @@ is the host-side mirror of the reference's interfaces for that path and nothing 
 from ._lib import (B200MoEError, BF16, F16, F32, FFN_AUTO, FFN_GEMV, FFN_MMA, W_DENSE, W_INT4_G128)
 from .activations import build_layer_activations
 from .context import MoEContext
+from .ingest import LayerSlab, ingest_layer
 from .layers import Qwen3MoEGate, Qwen3MoELayer, Qwen3MoELayerWithWeights, RMSNorm, expert_forward_with_weights
 from .runner import B200MoERunner
 from .types import AttentionOutput, ExpertActivation, ExpertID, LayerExpertActivations, ExpertPlacement, MoEShape, RoutingResult
 
 __all__ = [
     "B200MoEError", "MoEContext", "B200MoERunner", "Qwen3MoEGate", "Qwen3MoELayer", "Qwen3MoELayerWithWeights", "RMSNorm",
-    "expert_forward_with_weights", "build_layer_activations", "ExpertActivation", "LayerExpertActivations",
+    "expert_forward_with_weights", "build_layer_activations", "LayerSlab", "ingest_layer", "ExpertActivation", "LayerExpertActivations",
     "AttentionOutput", "ExpertID", "ExpertPlacement", "MoEShape", "RoutingResult",
     "F32", "F16", "BF16", "W_DENSE", "W_INT4_G128", "FFN_AUTO", "FFN_GEMV", "FFN_MMA",
 ]

@@ -124,3 +124,27 @@ def test_exact_logits_mode_reproduces_torch_router():
     vals, ids = torch.topk(torch.nn.functional.linear(x, gate_w), 8, dim=-1)
     assert torch.equal(r.topk_indices, ids)
     assert O.max_abs(r.topk_scores.float().cpu(), torch.softmax(vals, -1).float().cpu()) <= 2 ** -8
+
+
+@pytest.mark.parametrize("mode", ["dense", "int4"])
+def test_layer_slab_ingest_gives_identical_outputs(mode):
+    """All experts of a layer copied into one allocation (host fp32 sources): same bits as separate tensors."""
+    from on_device_sd_b200 import MoEContext, W_DENSE, W_INT4_G128, ingest_layer
+    from on_device_sd_b200.quant import quantize_expert
+    from on_device_sd_b200.synth import make_layer
+    H, E, K, I, T = 256, 8, 2, 128, 24
+    L = make_layer(H, E, K, I, torch.bfloat16, T, seed=41)
+    wm = W_INT4_G128 if mode == "int4" else W_DENSE
+    a = MoEContext(H, E, K, I, torch.bfloat16, max_tokens=32, weight_mode=wm)
+    b = MoEContext(H, E, K, I, torch.bfloat16, max_tokens=32, weight_mode=wm)
+    a.set_gate(0, L.gate_w.cuda()); b.set_gate(0, L.gate_w.cuda())
+    keep = []
+    for e, p in L.experts.items():
+        dev = {k: v.cuda() for k, v in p.items()}
+        keep.append(quantize_expert(dev) if mode == "int4" else dev)
+        a.set_expert(0, e, keep[-1])
+    slab = ingest_layer(b, 0, {e: {k: v.float() for k, v in p.items()} for e, p in L.experts.items()})   # CPU fp32 sources
+    assert slab.buffer.data_ptr() % 256 == 0 and len(slab.views) == E
+    x = L.x.cuda()
+    assert torch.equal(a.forward_fused(0, x), b.forward_fused(0, x))
+    assert a.status() == 0 and b.status() == 0
