@@ -568,8 +568,6 @@ template <typename T, int NT> static int launch_gemv_pair(b200moe_ctx* ctx, cons
   switch (ctx->gemv_variant) {   // tuning knob (environment variable B200MOE_GEMV_VARIANT at create time)
     case 1: return launch_gemv_pair_shape<T, NT, GemvShape<16, 1024, 3>>(ctx, p, st, s, which);
     case 2: return launch_gemv_pair_shape<T, NT, GemvShape<8, 1024, 6>>(ctx, p, st, s, which);
-    case 3: return launch_gemv_pair_shape<T, NT, GemvShape<8, 4096, 2>>(ctx, p, st, s, which);
-    case 4: return launch_gemv_pair_shape<T, NT, GemvShape<16, 2048, 2>>(ctx, p, st, s, which);
     default: return launch_gemv_pair_shape<T, NT, GemvDefault>(ctx, p, st, s, which);
   }
 }
