@@ -22,8 +22,8 @@
 // and only feed accumulator columns nobody reads.  No thread computes addresses per 16 bytes:
 // the integer pipe is what bounds this kernel (7 ALU operations per 8 weights for the nibbles).
 //
-//   warp 0      TMA producer, weights   warp 1      MMA issuer (even k-stages) + TMEM owner
-//   warp 2      TMA producer, tokens    warp 3      MMA issuer (odd k-stages)
+//   warp 0      TMA producer, weights   warp 2      TMA producer, tokens
+//   warps 1, 3  MMA issuers: issuer w takes the k-stages whose running index is w modulo 2 (warp 1 owns the TMEM allocation)
 //   warps 4-19  dequant: four groups of 4 warps; group g owns A stage g, i.e. every fourth k-stage,
 //               thread = one weight row of the stage (64 bytes of nibbles -> 64 columns)
 //   warps 20-23 epilogue
@@ -54,22 +54,27 @@ template <int NMAX> struct I4uShape {
   static constexpr int B_TILE = 2 * NMAX * 128;                 // two 64-k atoms of NMAX rows x 128 bytes
   static constexpr int W_STAGES = NMAX <= 16 ? 20 : (NMAX == 32 ? 16 : (NMAX == 64 ? 12 : 8));   // 8 KB each; a multiple of the number of dequant groups
   static constexpr int A_STAGES = kI4uAStages;
-  static constexpr int EX_BYTES = 64 * 17 * 4;
-  static constexpr int FIXED = 1024 + W_STAGES * kI4uWTile + EX_BYTES + 512;
-  static constexpr int B_FIT = (227 * 1024 - FIXED) / B_TILE;
-  static constexpr int B_STAGES = B_FIT > 8 ? 8 : B_FIT;
-  static constexpr size_t SMEM = (size_t)FIXED + (size_t)B_STAGES * B_TILE;
-  static constexpr int TMEM_COLS = 512;
   // Successive MMAs into one accumulator serialise on its latency, so the k-steps rotate over
   // PARTS independent accumulators that the epilogue adds up.
   static constexpr int PARTS = NMAX <= 32 ? 4 : (NMAX == 64 ? 2 : 1);
   // One warp issues a tcgen05.mma every 45-150 cycles depending on how the operands reach the
-  // uniform registers, the tensor pipe takes one every ~38: two issuing warps (even / odd k-stages,
-  // disjoint accumulators) keep the eight MMAs of a stage inside the stage's HBM time.
+  // uniform registers (measured in this kernel: ~75 per MMA), the tensor pipe takes one every ~38:
+  // two issuing warps on interleaved k-stages with disjoint accumulators keep the eight MMAs of a stage
+  // inside its HBM time (four issuers measured no faster: 80 against 83 k tokens/s on the Mixtral shape).
+  // Issuer w takes the stages whose RUNNING index (over the whole kernel) is w modulo MMA_WARPS: the ring
+  // depths are multiples of MMA_WARPS, so a ring slot always belongs to the same issuer and that issuer
+  // sees every phase of the slot's barriers (a warp that skipped a phase could not tell it from the next
+  // one of the same parity).
   static constexpr int MMA_WARPS = PARTS >= 2 ? 2 : 1;
   static constexpr int PARTS_PER_WARP = PARTS / MMA_WARPS;
+  static constexpr int EX_BYTES = 64 * 17 * 4;
+  static constexpr int FIXED = 1024 + W_STAGES * kI4uWTile + EX_BYTES + 512;
+  static constexpr int B_FIT = (227 * 1024 - FIXED) / B_TILE;
+  static constexpr int B_STAGES = (B_FIT > 8 ? 8 : B_FIT) / MMA_WARPS * MMA_WARPS;
+  static constexpr size_t SMEM = (size_t)FIXED + (size_t)B_STAGES * B_TILE;
+  static constexpr int TMEM_COLS = 512;
   static_assert(2 * PARTS * NMAX <= kI4uACol0, "accumulators overlap the A ring");
-  static_assert(B_STAGES >= 3, "token tile too large for the shared-memory budget");
+  static_assert(B_STAGES >= 3 && A_STAGES % MMA_WARPS == 0 && B_STAGES % MMA_WARPS == 0, "ring depths");
 };
 
 struct I4uParams {
@@ -192,7 +197,8 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
       const int e = warp_bcast(p.act_list[item / tiles]);
       const int tile = item % tiles;
       const int slot = st.slot[e];
-      const int n = warp_bcast(p.offsets[e + 1] - p.offsets[e]);
+      const int pos0 = warp_bcast(p.offsets[e]);
+      const int n = warp_bcast(p.offsets[e + 1]) - pos0;
       const CUtensorMap* m0 = ip.tmaps + (size_t)slot * 3 + (DUAL ? 0 : 2);
       const CUtensorMap* m1 = ip.tmaps + (size_t)slot * 3 + 1;
       tensormap_acquire(m0);
@@ -215,10 +221,10 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
     if (!ok && lane == 0) atomicOr(ip.status, kDevWaitExpired);
   } else if (warp == 2) {
     // ------------------------------ TMA producer: token tiles ------------------------------
-    const uint64_t policy = l2_policy_evict_last();      // every CTA working on this expert re-reads these rows
-    if (!DUAL) pdl_wait();                               // h must be complete; the weight stream above has already started
-    int s = 0;
-    uint32_t ph = 0;
+    const uint64_t policy_b = l2_policy_evict_last();    // every CTA working on this expert re-reads the token rows
+    if (!DUAL) pdl_wait();                               // h must be complete; the weight stream has already started
+    int sb = 0;
+    uint32_t phb = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
       const int e = warp_bcast(p.act_list[item / tiles]);
@@ -226,25 +232,25 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
       const int n = warp_bcast(p.offsets[e + 1]) - pos0;
       for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
         for (int kb = 0; kb < nkb; ++kb) {
-          if (!__all_sync(0xffffffffu, wait_or_abort(&b_empty[s], ph ^ 1, abort_flag))) { ok = false; break; }
+          if (!__all_sync(0xffffffffu, wait_or_abort(&b_empty[sb], phb ^ 1, abort_flag))) { ok = false; break; }
           const int npad = (min(NMAX, n - c0) + 15) & ~15;
-          mbar_expect_tx_w(&b_full[s], (uint32_t)(2 * npad * 128));
-          unsigned char* dst = Bs + (size_t)s * B_TILE;
+          mbar_expect_tx_w(&b_full[sb], (uint32_t)(2 * npad * 128));
+          unsigned char* bdst = Bs + (size_t)sb * B_TILE;
           for (int r = 0; r < npad; r += 16) {   // boxes of 16 rows: only the rows this pass multiplies are fetched
-            tma_load_2d_w(dst + r * 128, &ip.bmap, kb * kI4uBK, pos0 + c0 + r, &b_full[s], policy);
-            tma_load_2d_w(dst + NMAX * 128 + r * 128, &ip.bmap, kb * kI4uBK + 64, pos0 + c0 + r, &b_full[s], policy);
+            tma_load_2d_w(bdst + r * 128, &ip.bmap, kb * kI4uBK, pos0 + c0 + r, &b_full[sb], policy_b);
+            tma_load_2d_w(bdst + NMAX * 128 + r * 128, &ip.bmap, kb * kI4uBK + 64, pos0 + c0 + r, &b_full[sb], policy_b);
           }
-          if (++s == BSTAGES) { s = 0; ph ^= 1; }
+          if (++sb == BSTAGES) { sb = 0; phb ^= 1; }
         }
       }
     }
     if (!ok && lane == 0) atomicOr(ip.status, kDevWaitExpired);
   } else if (warp == 1 || warp == 3) {
     // ------------------------------ MMA issuers (whole warps, warp-uniform; see tc_mma_bf16_w) ------------------------------
-    // Issuer w takes the k-stages of a job with kb % MMA_WARPS == w and owns PARTS_PER_WARP accumulators.
+    // Issuer w takes the k-stages whose running index is w modulo MMA_WARPS and owns PARTS_PER_WARP accumulators.
     const int w = warp == 1 ? 0 : 1;
     if (w < S::MMA_WARPS) {
-      int s = 0, sb = 0, job = 0;
+      int s = 0, sb = 0, job = 0, gmod = 0;      // gmod: running stage index modulo MMA_WARPS
       uint32_t ph = 0, phb = 0;
       bool ok = true;
       for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
@@ -257,13 +263,13 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
           if (!__all_sync(0xffffffffu, wait_or_abort(&acc_empty[b], ((job >> 1) & 1) ^ 1, abort_flag))) { ok = false; break; }
           tc_fence_after();
           const uint32_t d_tmem = tmem_base + (uint32_t)((b * S::PARTS + w * S::PARTS_PER_WARP) * NMAX);
+          uint32_t started = 0u;                  // this issuer's first stage of the job starts its accumulators
           for (int kb = 0; kb < nkb; ++kb) {
-            if ((kb % S::MMA_WARPS) == w) {
+            if (gmod == w) {
               const bool got = wait_or_abort(&full[s], ph, abort_flag) && wait_or_abort(&b_full[sb], phb, abort_flag);
               if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
               tc_fence_after();
               const uint32_t a_tmem = tmem_base + (uint32_t)(kI4uACol0 + s * kI4uACols);
-              const uint32_t first = kb < S::MMA_WARPS ? 0u : 1u;      // this issuer's first stage of the job starts its accumulators
 #pragma unroll
               for (int atom = 0; atom < 2; ++atom) {
                 const uint64_t bdesc = umma_desc_sw128(smem_addr(Bs + (size_t)sb * B_TILE + atom * NMAX * 128));
@@ -271,12 +277,14 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
                 for (int k = 0; k < 4; ++k) {   // 16 k per MMA = 8 columns of A
                   const int kk = atom * 4 + k;
                   tc_mma_bf16_ts_w(d_tmem + (uint32_t)((kk % S::PARTS_PER_WARP) * NMAX), a_tmem + (uint32_t)(kk * 8), bdesc + 2 * k, idesc,
-                                   kk >= S::PARTS_PER_WARP ? 1u : first);
+                                   kk >= S::PARTS_PER_WARP ? 1u : started);
                 }
               }
+              started = 1u;
               tc_commit_w(&empty[s]);
               tc_commit_w(&b_empty[sb]);
             }
+            if (++gmod == S::MMA_WARPS) gmod = 0;
             if (++s == STAGES) { s = 0; ph ^= 1; }
             if (++sb == BSTAGES) { sb = 0; phb ^= 1; }
           }
@@ -362,7 +370,7 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
     // ------------------------------ epilogue ------------------------------
     const int q = warp & 3;                       // TMEM lane quarter this warp may read
     const int et = threadIdx.x - kI4uFirstEpi * 32;   // 0..127
-    int job = 0;
+    int job = 0, gbase = 0;                       // gbase: running index of the job's first k-stage modulo MMA_WARPS
     bool ok = true;
     __nv_bfloat16* hout = reinterpret_cast<__nv_bfloat16*>(p.h);
     __nv_bfloat16* yout = reinterpret_cast<__nv_bfloat16*>(p.y);
@@ -382,17 +390,24 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
         if (!ok) break;
         tc_fence_after();
         for (int col = 0; col < npad; col += 16) {
+          // Sum of the accumulators, in part order.  A job with fewer k-stages than issuers leaves the
+          // accumulators of the idle issuers untouched: issuer w worked iff (w - gbase) mod MMA_WARPS < nkb.
           uint32_t r[16];
-          tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(b * S::PARTS * NMAX + col), r);
-          // with a single k-stage the second issuer never started its accumulators
-          const int parts = (S::MMA_WARPS > 1 && nkb < S::MMA_WARPS) ? S::PARTS_PER_WARP : S::PARTS;
+          bool have = false;
 #pragma unroll
-          for (int part = 1; part < S::PARTS; ++part) {
-            if (part >= parts) break;
+          for (int part = 0; part < S::PARTS; ++part) {
+            const int wi = part / S::PARTS_PER_WARP;
+            if (((wi - gbase + S::MMA_WARPS) % S::MMA_WARPS) >= nkb) continue;
             uint32_t r2[16];
             tc_ld16(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)((b * S::PARTS + part) * NMAX + col), r2);
+            if (!have) {
 #pragma unroll
-            for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(r2[j])));
+              for (int j = 0; j < 16; ++j) r[j] = r2[j];
+              have = true;
+            } else {
+#pragma unroll
+              for (int j = 0; j < 16; ++j) r[j] = __float_as_uint(__fadd_rn(__uint_as_float(r[j]), __uint_as_float(r2[j])));
+            }
           }
           if (DUAL) {
             if (q >= 2) {
@@ -427,6 +442,7 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
         }
         tc_fence_before();
         mbar_arrive(&acc_empty[b]);
+        gbase = (gbase + nkb) % S::MMA_WARPS;
       }
     }
     if (!ok && et == 0) atomicOr(ip.status, kDevWaitExpired);

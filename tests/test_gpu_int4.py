@@ -125,3 +125,16 @@ def test_int4_popular_expert_exceeds_the_token_tile():
     out = ctx.forward(0, L.x.cuda(), ids.cuda(), sc.cuda())
     assert ctx.status() == 0
     _close(out, O.moe_engine(L.x, ids, sc, deq, order=[5, 9]), torch.bfloat16, tight=True)
+
+
+@pytest.mark.gpu
+@pytest.mark.parametrize("T", [3, 24, 70])
+def test_int4_odd_number_of_k_stages(T):
+    """H = 384 and I = 640 give 3 and 5 k-stages of 128 per work item: the two MMA issuers alternate over the
+    running stage index, so which issuer starts a work item changes from item to item."""
+    H, E, K, I = 384, 8, 2, 640
+    L, ctx, deq = _int4_layer(H, E, K, I, T, seed=37)
+    out, ids, scores = ctx.forward_fused(0, L.x.cuda(), return_routing=True)
+    assert ctx.status() == 0
+    want = O.moe_engine(L.x, ids.cpu(), scores.cpu(), deq, order=sorted(set(ids.flatten().tolist())))
+    _close(out, want, torch.bfloat16, tight=True)
