@@ -486,27 +486,13 @@ def run_ep(args, workload):
                 eager(T)
         torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
         side = torch.cuda.Stream(device=dev)
-        dbg = os.environ.get("B200MOE_BENCH_DEBUG")
         for T in batches:
-            if dbg: print(f"[rank {rank}] capturing T={T}", file=sys.stderr, flush=True)
             g_ = torch.cuda.CUDAGraph()
             with torch.cuda.graph(g_, stream=side, capture_error_mode="thread_local"):
                 out_ = eager(T)
             graphs[T] = (g_, out_)
-            if dbg: print(f"[rank {rank}] captured T={T}", file=sys.stderr, flush=True)
         torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
-        if dbg:
-            for T in batches:
-                graphs[T][0].replay(); torch.cuda.synchronize()
-                print(f"[rank {rank}] replayed T={T}", file=sys.stderr, flush=True)
-    if graphs and os.environ.get("B200MOE_BENCH_SYNC"):
-        def one(T):
-            graphs[T][0].replay(); torch.cuda.current_stream().synchronize()
-    else:
-        one = (lambda T: graphs[T][0].replay()) if graphs else eager
-    if os.environ.get("B200MOE_BENCH_DEBUG"):
-        import faulthandler
-        faulthandler.dump_traceback_later(45, exit=False, file=sys.stderr)
+    one = (lambda T: graphs[T][0].replay()) if graphs else eager
     def step():
         for T in batches:
             one(T)
