@@ -227,7 +227,8 @@ def run_ours(args, workload):
     shape = MoEShape(H, E, K, I, "bfloat16")
     from on_device_sd_b200 import FFN_AUTO, FFN_GEMV, FFN_MMA
     kind = {"auto": FFN_AUTO, "gemv": FFN_GEMV, "mma": FFN_MMA}[args.ffn_kind]
-    runner = B200MoERunner(shape, device=dev, max_tokens=max(batches), weight_mode=W_INT4_G128 if int4 else W_DENSE, ffn_kind=kind)
+    runner = B200MoERunner(shape, device=dev, max_tokens=max(batches), weight_mode=W_INT4_G128 if int4 else W_DENSE, ffn_kind=kind,
+                           graph_blocks=not args.no_graph)
     runner.load_gate(0, L.gate_w)
     dense_experts = L.experts
     if int4:
@@ -412,7 +413,7 @@ def run_ours(args, workload):
                    "l2": "expert weights of one step (0.7-2.8 GB for mixtral) exceed the 126 MB L2, no flush needed" if cfg_name == "mixtral"
                          else "weights of the larger batches exceed L2; the smallest batches can be L2-resident"},
         "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": tokens_per_step * H * 2, "d2h_bytes_per_step": tokens_per_step * H * 2,
-                "api": "B200MoERunner.moe_block with pinned host buffers, one synchronize per step"},
+                "api": "B200MoERunner(graph_blocks=%s).moe_block with pinned host buffers: H2D copy, block, D2H copy per batch, one synchronize per step" % (not args.no_graph)},
         "gpu_launches": launches, "clocks": clocks, "roofline": roofline, "cpu_baseline": cpu, "per_T": per_T,
     }
     print(json.dumps(line), flush=True)

@@ -71,14 +71,19 @@ def plan_placement(expert_placement: Any, num_experts: int):
 class B200MoERunner:
     def __init__(self, config: Any, *, device: Optional[torch.device] = None, max_tokens: int = 512,
                  weight_mode: int = W_DENSE, expert_id_cls: type = ExpertID, exact_logits: bool = False,
-                 ffn_kind: int = FFN_AUTO):
+                 ffn_kind: int = FFN_AUTO, graph_blocks: bool = False):
         """`config` is the reference's MoEConfig or anything with hidden_size, num_experts,
         num_experts_per_token, moe_intermediate_size, num_hidden_layers and get_dtype().
 
         exact_logits=True computes the gate GEMM with torch's F.linear (the library GEMM the
         reference calls, moe_layer.py:44) and runs only top-k/softmax here, which reproduces the
         reference's logits roundings on the same GPU; the default computes the logits in the
-        fused router kernel as correctly rounded dot products."""
+        fused router kernel as correctly rounded dot products.
+
+        graph_blocks=True makes `moe_block` capture its kernels into a CUDA graph the first time it sees
+        an input buffer (keyed by layer, address, shape and residual address) and replay it afterwards:
+        one launch per block instead of five.  The result then lives in a buffer owned by the runner that
+        the next call with the same key overwrites, and the experts must not be re-registered in between."""
         self.config = config
         self.dtype = config.get_dtype()
         self.expert_id_cls = expert_id_cls
@@ -91,6 +96,8 @@ class B200MoERunner:
         self._bitmap = torch.zeros(4, dtype=torch.int64).pin_memory()
         self._gate_w: Dict[int, torch.Tensor] = {}
         self._last_layer = 0
+        self.graph_blocks = graph_blocks
+        self._graphs: Dict[tuple, tuple] = {}
 
     def get_config(self):
         return self.config
@@ -176,6 +183,20 @@ class B200MoERunner:
         h = hidden_states.shape[-1]
         flat = hidden_states.reshape(-1, h)
         res2d = None if residual is None else residual.reshape(-1, h)
+        if self.graph_blocks and not return_routing and flat.is_contiguous() and (res2d is None or res2d.is_contiguous()):
+            key = (layer_idx, flat.data_ptr(), tuple(flat.shape), None if res2d is None else res2d.data_ptr())
+            hit = self._graphs.get(key)
+            if hit is None:
+                for _ in range(2):                       # warm-up outside the capture (lazy kernel attributes, tensor maps)
+                    self.ctx.forward_fused(layer_idx, flat, residual=res2d, ffn_kind=self.ffn_kind)
+                torch.cuda.current_stream(self.device).synchronize()
+                g = torch.cuda.CUDAGraph()
+                with torch.cuda.graph(g):
+                    out = self.ctx.forward_fused(layer_idx, flat, residual=res2d, ffn_kind=self.ffn_kind)
+                hit = (g, out)
+                self._graphs[key] = hit
+            hit[0].replay()
+            return hit[1].view(hidden_states.shape)
         r = self.ctx.forward_fused(layer_idx, flat, residual=res2d, return_routing=return_routing, ffn_kind=self.ffn_kind)
         if return_routing:
             return r[0].view(hidden_states.shape), r[1], r[2]

@@ -148,3 +148,25 @@ def test_layer_slab_ingest_gives_identical_outputs(mode):
     x = L.x.cuda()
     assert torch.equal(a.forward_fused(0, x), b.forward_fused(0, x))
     assert a.status() == 0 and b.status() == 0
+
+
+def test_moe_block_graph_replay_equals_eager_launches():
+    """B200MoERunner(graph_blocks=True): the captured block replays with new contents of the same input buffer."""
+    from on_device_sd_b200 import B200MoERunner, MoEShape
+    from on_device_sd_b200.synth import make_layer
+    H, E, K, I, T = 256, 8, 2, 128, 12
+    L = make_layer(H, E, K, I, torch.bfloat16, T, seed=43)
+    shape = MoEShape(H, E, K, I, "bfloat16", 1)
+    eager = B200MoERunner(shape, max_tokens=16)
+    graphed = B200MoERunner(shape, max_tokens=16, graph_blocks=True)
+    for r in (eager, graphed):
+        r.load_gate(0, L.gate_w.cuda())
+        r.register_experts(0, {e: {k: v.cuda() for k, v in p.items()} for e, p in L.experts.items()})
+    x = L.x.cuda().clone()
+    res = torch.randn_like(x)
+    for trial in range(3):
+        want = eager.moe_block(0, x, residual=res)
+        got = graphed.moe_block(0, x, residual=res)
+        assert torch.equal(got, want), trial
+        x.copy_(torch.randn(T, H, generator=torch.Generator().manual_seed(trial)).bfloat16())   # same buffer, new tokens
+    assert len(graphed._graphs) == 1 and eager.ctx.status() == 0 and graphed.ctx.status() == 0
