@@ -10,6 +10,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <algorithm>
+#include <atomic>
 #include <new>
 #include <string>
 #include <utility>
@@ -535,6 +536,14 @@ struct FfnLaunch {
   bool ksplit_ok = false;   // the consumer of y accepts fp32 K-slices (the combine kernel does)
 };
 
+// The opt-in dynamic shared-memory size is a property of a kernel ON ONE DEVICE: remember per template
+// instance which devices have been configured (one bit each), not just that some device was.
+struct ConfiguredDevices {
+  std::atomic<unsigned long long> mask{0};
+  bool needs(int device) const { return device < 0 || device >= 64 || !((mask.load(std::memory_order_acquire) >> device) & 1ull); }
+  void done(int device) { if (device >= 0 && device < 64) mask.fetch_or(1ull << device, std::memory_order_release); }
+};
+
 using GemvDefault = GemvShape<8, 2048, 3>;
 
 // which: bit 0 = gate/up projection, bit 1 = down projection
@@ -542,11 +551,11 @@ template <typename T, int NT, typename S> static int launch_gemv_pair_shape(b200
   const int grid = ctx->sm_count;   // one persistent CTA per SM: the rings take most of its shared memory
   auto up = ffn_gemv_kernel<T, NT, true, S>;
   auto down = ffn_gemv_kernel<T, NT, false, S>;
-  static bool configured = false;   // per template instance
-  if (!configured) {
+  static ConfiguredDevices configured;   // per template instance
+  if (configured.needs(ctx->cfg.device)) {
     CUDA_TRY(ctx, cudaFuncSetAttribute(up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
     CUDA_TRY(ctx, cudaFuncSetAttribute(down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
-    configured = true;
+    configured.done(ctx->cfg.device);
   }
   if (which & 1) {
     {
@@ -577,11 +586,11 @@ template <typename T, int NMAX> static int launch_umma_pair(b200moe_ctx* ctx, co
   using S = UmmaShape<NMAX>;
   auto k_up = ffn_umma_kernel<T, NMAX, true>;
   auto k_down = ffn_umma_kernel<T, NMAX, false>;
-  static bool configured = false;
-  if (!configured) {
+  static ConfiguredDevices configured;   // per template instance
+  if (configured.needs(ctx->cfg.device)) {
     CUDA_TRY(ctx, cudaFuncSetAttribute(k_up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
     CUDA_TRY(ctx, cudaFuncSetAttribute(k_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
-    configured = true;
+    configured.done(ctx->cfg.device);
   }
   if (which & 1) {
     {
@@ -637,11 +646,11 @@ static int launch_ffn_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tma
 template <int NTILE> static int launch_int4_pair(b200moe_ctx* ctx, const Int4Params& ip, const SlotTable& st, cudaStream_t s) {
   auto k_up = ffn_int4_kernel<true, NTILE>;
   auto k_down = ffn_int4_kernel<false, NTILE>;
-  static bool configured = false;
-  if (!configured) {
+  static ConfiguredDevices configured;   // per template instance
+  if (configured.needs(ctx->cfg.device)) {
     CUDA_TRY(ctx, cudaFuncSetAttribute(k_up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kInt4Smem));
     CUDA_TRY(ctx, cudaFuncSetAttribute(k_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kInt4Smem));
-    configured = true;
+    configured.done(ctx->cfg.device);
   }
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
@@ -660,11 +669,11 @@ template <int NMAX> static int launch_i4u_pair(b200moe_ctx* ctx, const I4uParams
   using S = I4uShape<NMAX>;
   auto k_up = ffn_int4_umma_kernel<NMAX, true>;
   auto k_down = ffn_int4_umma_kernel<NMAX, false>;
-  static bool configured = false;
-  if (!configured) {
+  static ConfiguredDevices configured;   // per template instance
+  if (configured.needs(ctx->cfg.device)) {
     CUDA_TRY(ctx, cudaFuncSetAttribute(k_up, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
     CUDA_TRY(ctx, cudaFuncSetAttribute(k_down, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM));
-    configured = true;
+    configured.done(ctx->cfg.device);
   }
   {
     ProfScope prof(ctx, B200MOE_KERNEL_FFN_GATEUP, s);
