@@ -2,7 +2,8 @@
 
 TEST INFRASTRUCTURE.  Run in a container that has the reference checked out:
 
-    python oracle/pin_against_reference.py [--reference /root/reference]
+    python oracle/pin_against_reference.py --reference <checkout of potatoZhx/on_device_sd>
+    (or set ON_DEVICE_SD_REFERENCE to that directory)
 
 It imports the reference's own modules (demo/src/layers/moe_layer.py, demo/src/model/
 qwen3_runner.py, demo/src/core/*) on the CPU, runs both of its MoE paths on seeded inputs and
@@ -16,6 +17,7 @@ so these fixtures are the pin.
 from __future__ import annotations
 
 import argparse
+import os
 import hashlib
 import sys
 import types
@@ -49,7 +51,8 @@ def digest(layer) -> str:
 
 def main() -> None:
     ap = argparse.ArgumentParser()
-    ap.add_argument("--reference", default="/root/reference")
+    ap.add_argument("--reference", default=os.environ.get("ON_DEVICE_SD_REFERENCE"), required=os.environ.get("ON_DEVICE_SD_REFERENCE") is None,
+                    help="directory of the reference checkout (the one that contains demo/)")
     args = ap.parse_args()
     sys.path.insert(0, str(Path(args.reference) / "demo"))
     from src.core.model_runner import AttentionOutput, ExpertPlacement, RoutingResult  # type: ignore
