@@ -36,35 +36,51 @@ def plan_placement(expert_placement: Any, num_experts: int):
       slot   slot[e] = expert whose parameters serve tokens routed to e: e itself, else its
              substitute from substitution_map (with the ORIGINAL routing weight, :322-329), else -1
              = skipped silently (:330-333).  Only activated experts get a slot.
-      order  order[e] = position of e in the iteration of routing.activated_expert_ids, the order
-             in which the reference accumulates per-expert results in the model dtype (:303, :376)
+      order  order[e] = position of e in the sequence in which the reference accumulates the
+             per-expert results in the model dtype: every expert served from gpu_expert_params
+             (directly or through its substitute) in the iteration order of
+             routing.activated_expert_ids, THEN every expert served from cpu_expert_params in that
+             same iteration order (the reference collects gpu_tasks and cpu_tasks in one pass, :303-333,
+             and adds all GPU results before the CPU results, :352-383)
     """
     routing = expert_placement.routing_result
     E = num_experts
-    avail: Dict[int, Dict[str, torch.Tensor]] = {}
-    for src in (expert_placement.cpu_expert_params, expert_placement.gpu_expert_params):
-        for e, params in (src or {}).items():
-            avail[e] = params
+    gpu = expert_placement.gpu_expert_params or {}
+    cpu = expert_placement.cpu_expert_params or {}
+    avail: Dict[int, Dict[str, torch.Tensor]] = dict(cpu)
+    avail.update(gpu)
     slot = [-1] * E
     sub = expert_placement.substitution_map or {}
-    order = [0] * E
-    ranked = [False] * E
-    seen = 0
+    first: List[int] = []      # served from GPU-resident parameters
+    second: List[int] = []     # served from CPU-resident parameters
+    skipped: List[int] = []
+    seen = [False] * E
     for eid in routing.activated_expert_ids:
         e = eid.expert_idx
-        if not 0 <= e < E:
+        if not 0 <= e < E or seen[e]:
             continue
-        if e in avail:
+        seen[e] = True
+        if e in gpu:
             slot[e] = e
-        elif e in sub and sub[e] in avail:
+            first.append(e)
+        elif e in cpu:
+            slot[e] = e
+            second.append(e)
+        elif e in sub and sub[e] in gpu:
             slot[e] = sub[e]
-        if not ranked[e]:
-            order[e] = seen
-            ranked[e] = True
-            seen += 1
+            first.append(e)
+        elif e in sub and sub[e] in cpu:
+            slot[e] = sub[e]
+            second.append(e)
+        else:
+            skipped.append(e)
+    order = [0] * E
+    ranked = first + second + skipped
+    for r, e in enumerate(ranked):
+        order[e] = min(r, 255)
     for e in range(E):
-        if not ranked[e]:
-            order[e] = min(seen, 255)
+        if not seen[e]:
+            order[e] = min(len(ranked), 255)
     return avail, slot, order
 
 

@@ -255,31 +255,41 @@ def expert_ffn(x: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor, 
 
 def moe_engine(x: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, experts: Dict[int, ExpertParams], *,
                layer_idx: int = 0, substitution: Optional[Dict[int, int]] = None,
-               order: Optional[Sequence[int]] = None, residual: Optional[torch.Tensor] = None) -> torch.Tensor:
-    """Path B: qwen3_runner.py:269-385 with every supplied expert resident on x's device.
+               order: Optional[Sequence[int]] = None, residual: Optional[torch.Tensor] = None,
+               cpu_experts: Optional[Dict[int, ExpertParams]] = None) -> torch.Tensor:
+    """Path B: qwen3_runner.py:269-385.  `experts` plays gpu_expert_params, `cpu_experts` plays
+    cpu_expert_params (both evaluated on x's device here: where an expert's arithmetic runs does not
+    change the algorithm, only which of the two task lists it joins).
 
-    For each activated expert, in set-iteration order: (tok, k) = where(ids == e) in row-major
-    order, y = FFN(x[tok]), final[tok] += y * scores[tok, k][:, None]  (index-put without
-    accumulation for repeated tok, exactly as torch does for `a[idx] += b`).  An expert with
-    neither parameters nor a usable substitute is skipped (:330-333).  `residual` adds
+    One pass over the activated experts in set-iteration order (:303) sorts them into GPU tasks and
+    CPU tasks - own GPU parameters, else own CPU parameters, else the substitute's GPU parameters,
+    else the substitute's CPU parameters, else skipped (:316-333).  (tok, k) = where(ids == e) in
+    row-major order, y = FFN(x[tok]), final[tok] += y * scores[tok, k][:, None]  (index-put without
+    accumulation for repeated tok, exactly as torch does for `a[idx] += b`); every GPU task is
+    accumulated before any CPU task (:352-383), each list in its collection order.  `residual` adds
     forward_moe's residual (:226).
     """
     shape = x.shape
     flat = x.reshape(-1, shape[-1])
     final = torch.zeros_like(flat)
     sub = substitution or {}
+    cpu = cpu_experts or {}
     if order is None:
         order = activated_order(layer_idx, ids)
+    gpu_tasks, cpu_tasks = [], []
     for e in order:
         tok, kk = torch.where(ids == e)
         if tok.numel() == 0:
             continue
         if e in experts:
-            p = experts[e]
+            gpu_tasks.append((tok, kk, experts[e]))
+        elif e in cpu:
+            cpu_tasks.append((tok, kk, cpu[e]))
         elif e in sub and sub[e] in experts:
-            p = experts[sub[e]]
-        else:
-            continue
+            gpu_tasks.append((tok, kk, experts[sub[e]]))
+        elif e in sub and sub[e] in cpu:
+            cpu_tasks.append((tok, kk, cpu[sub[e]]))
+    for tok, kk, p in gpu_tasks + cpu_tasks:
         w = scores[tok, kk]
         y = expert_ffn(flat[tok], p["gate_proj"].to(flat.dtype), p["up_proj"].to(flat.dtype), p["down_proj"].to(flat.dtype))
         final[tok] += y * w.unsqueeze(1)

@@ -163,6 +163,33 @@ def main() -> None:
     np.savez_compressed(golden / "placement_fp16.npz", **rec)
     print("placement_fp16: substitution / skip / fp32-score semantics == reference bit for bit")
 
+    # mixed GPU-resident / CPU-resident placement with top-4 routing: the reference adds every GPU task
+    # before any CPU task (demo/src/model/qwen3_runner.py:352-383), so the bf16 accumulation order is
+    # "GPU-served experts in set order, then CPU-served experts in set order"
+    layer = make_layer(64, 12, 4, 32, torch.bfloat16, 10, seed=6)
+    r = reference_runner(layer, 2)
+    with torch.no_grad():
+        routing = r.route_experts(2, layer.x)
+        gpu_p = {e: layer.experts[e] for e in (0, 3, 4, 7, 8, 11)}
+        cpu_p = {e: layer.experts[e] for e in (1, 2, 5, 7)}                  # 7 is in both: the GPU copy wins
+        subm = {6: 1, 9: 4, 10: 10}                                          # 6 -> CPU-resident 1, 9 -> GPU-resident 4, 10 -> nothing usable
+        pl = ExpertPlacement(gpu_expert_params=gpu_p, cpu_expert_params=cpu_p, substitution_map=subm, routing_result=routing)
+        ref = r._execute_moe_with_placement(layer.x, pl)
+        ref_order = [eid.expert_idx for eid in routing.activated_expert_ids]
+        mine = O.moe_engine(layer.x, routing.topk_indices, routing.topk_scores, gpu_p, layer_idx=2, substitution=subm, cpu_experts=cpu_p)
+        assert torch.equal(ref, mine), O.max_abs(ref, mine)
+        plain = O.moe_engine(layer.x, routing.topk_indices, routing.topk_scores, {**cpu_p, **gpu_p}, layer_idx=2, substitution=subm)
+        assert not torch.equal(ref, plain)      # the case does distinguish the two orders
+    rec = dict(seed=6, layer_idx=2, gate_w=to_np(layer.gate_w), x=to_np(layer.x), ids=routing.topk_indices.numpy(),
+               scores=to_np(routing.topk_scores), ref_out=to_np(ref), ref_order=np.array(ref_order),
+               gpu_experts=np.array(sorted(gpu_p)), cpu_experts=np.array(sorted(cpu_p)),
+               sub_from=np.array(sorted(subm)), sub_to=np.array([subm[k] for k in sorted(subm)]))
+    for e in layer.experts:
+        for k, v in layer.experts[e].items():
+            rec[f"expert{e}_{k}"] = to_np(v)
+    np.savez_compressed(golden / "mixed_placement_bf16.npz", **rec)
+    print("mixed_placement_bf16: GPU tasks before CPU tasks == reference bit for bit (and differs from plain set order)")
+
     # LayerExpertActivations (demo/src/execution/model_runner_utils.py:13-41) on a routed batch
     from src.execution.model_runner_utils import build_layer_activations
     layer = make_layer(64, 16, 4, 32, torch.bfloat16, 40, seed=5)

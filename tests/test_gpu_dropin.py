@@ -83,6 +83,23 @@ def test_substitution_uses_substitute_params(small):
     assert O.max_abs(out.cpu(), want) <= 1e-3 and out.abs().sum() > 0
 
 
+def test_mixed_gpu_cpu_placement_matches_reference_fixture():
+    """A placement mixing GPU-resident, CPU-resident and substituted experts with top-4 routing: the
+    reference's own output (fixture) within the same-order tolerance, i.e. GPU tasks accumulate first."""
+    from on_device_sd_b200 import B200MoERunner, ExpertID, ExpertPlacement, MoEShape, RoutingResult
+    from test_oracle_golden import load_mixed_placement
+    m = load_mixed_placement()
+    runner = B200MoERunner(MoEShape(64, 12, 4, 32, "bfloat16", num_hidden_layers=3), max_tokens=16)
+    act = set()
+    for e in m["ids"].flatten().unique().tolist():
+        act.add(ExpertID(m["layer_idx"], int(e)))
+    r = RoutingResult(m["layer_idx"], m["ids"].cuda(), m["scores"].cuda(), act)
+    gpu = {e: {k: v.cuda() for k, v in p.items()} for e, p in m["gpu"].items()}
+    out = runner._execute_moe_with_placement(m["x"].cuda(), ExpertPlacement(gpu, m["cpu"], m["sub"], r))
+    assert runner.ctx.status() == 0
+    assert O.mean_rel(out.cpu(), m["ref"]) <= 1e-3 and O.max_abs(out.cpu(), m["ref"]) <= 2e-2
+
+
 def test_module_dropins_match_oracle():
     from on_device_sd_b200 import Qwen3MoEGate, Qwen3MoELayer, Qwen3MoELayerWithWeights
     from on_device_sd_b200.synth import make_layer

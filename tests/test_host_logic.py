@@ -44,6 +44,31 @@ def test_plan_placement_substitution_skip_and_cpu_params():
     assert plan_placement(p, 4)[1] == [0, -1, -1, -1]    # substitute absent too -> skipped silently
 
 
+def test_plan_placement_ranks_gpu_served_experts_before_cpu_served_ones():
+    """The reference adds every GPU task before any CPU task (qwen3_runner.py:352-383): on its own mixed
+    fixture the rank table must reproduce that sequence, which the oracle then turns into the stored output."""
+    from test_oracle_golden import load_mixed_placement
+    m = load_mixed_placement()
+    act = set()
+    for e in m["ids"].flatten().unique().tolist():
+        act.add(ExpertID(m["layer_idx"], int(e)))
+    r = RoutingResult(m["layer_idx"], m["ids"], m["scores"], act)
+    avail, slot, order = plan_placement(ExpertPlacement(m["gpu"], m["cpu"], m["sub"], r), 12)
+    visit = [eid.expert_idx for eid in act]
+    assert visit == m["order"]
+    gpu_served = [e for e in visit if e in m["gpu"] or (e not in m["cpu"] and m["sub"].get(e) in m["gpu"])]
+    cpu_served = [e for e in visit if e not in gpu_served and (e in m["cpu"] or m["sub"].get(e) in m["cpu"])]
+    assert cpu_served and gpu_served
+    for rank, e in enumerate(gpu_served + cpu_served):
+        assert order[e] == rank
+    assert slot[6] == 1 and slot[9] == 4 and slot[10] == -1 and avail[7] is m["gpu"][7]     # resident in both: the GPU copy wins
+    # the oracle, driven by that sequence and nothing else, reproduces the reference's output bit for bit
+    served = {**m["cpu"], **m["gpu"]}
+    table = {e: served[slot[e]] for e in visit if slot[e] >= 0}
+    out = O.moe_engine(m["x"], m["ids"], m["scores"], table, order=sorted(table, key=lambda e: order[e]))
+    assert torch.equal(out, m["ref"])
+
+
 def test_synth_is_deterministic_and_distributed_as_stated():
     a = make_layer(64, 4, 2, 32, torch.bfloat16, 5, seed=0)
     b = make_layer(64, 4, 2, 32, torch.bfloat16, 5, seed=0)

@@ -122,3 +122,22 @@ def test_rmsnorm_restatement_matches_reference_fixture():
         assert torch.equal(O.rmsnorm(x, w, 1e-6), from_np(z[f"{name}_out"], dt))
         out, res = O.rmsnorm(x, w, 1e-6, r)
         assert torch.equal(out, from_np(z[f"{name}_out_add"], dt)) and torch.equal(res, from_np(z[f"{name}_res"], dt))
+
+
+def load_mixed_placement():
+    """Fixture written from the reference's _execute_moe_with_placement on a placement that mixes
+    GPU-resident and CPU-resident experts (demo/src/model/qwen3_runner.py:298-383)."""
+    z = np.load(GOLDEN / "mixed_placement_bf16.npz")
+    bf = torch.bfloat16
+    experts = {e: {k: from_np(z[f"expert{e}_{k}"], bf) for k in ("gate_proj", "up_proj", "down_proj")} for e in range(12)}
+    return dict(z=z, x=from_np(z["x"], bf), ids=torch.from_numpy(z["ids"].astype(np.int64)), scores=from_np(z["scores"], bf),
+                gpu={int(e): experts[int(e)] for e in z["gpu_experts"]}, cpu={int(e): experts[int(e)] for e in z["cpu_experts"]},
+                sub={int(a): int(b) for a, b in zip(z["sub_from"], z["sub_to"])}, ref=from_np(z["ref_out"], bf),
+                order=z["ref_order"].tolist(), layer_idx=int(z["layer_idx"]))
+
+
+def test_oracle_mixed_placement_accumulates_gpu_tasks_first():
+    m = load_mixed_placement()
+    assert O.activated_order(m["layer_idx"], m["ids"]) == m["order"]
+    out = O.moe_engine(m["x"], m["ids"], m["scores"], m["gpu"], layer_idx=m["layer_idx"], substitution=m["sub"], cpu_experts=m["cpu"])
+    assert torch.equal(out, m["ref"])
