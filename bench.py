@@ -422,8 +422,9 @@ def run_ours(args, workload):
 
 
 def run_ep(args, workload):
-    """Expert-parallel layer: experts sharded over the ranks, all-gather dispatch and reduce-scatter
-    return over NCCL (on_device_sd_b200/ep.py).  Eager launches; time = max over ranks, device events."""
+    """Expert-parallel layer: experts sharded over the ranks, token rows and results exchanged by the
+    library's own kernels through peer memory (on_device_sd_b200/ep.py).  Eager launches; time = max over
+    ranks, device events."""
     import torch.distributed as dist
     from on_device_sd_b200 import MoEContext, W_DENSE, W_INT4_G128
     from on_device_sd_b200.ep import ExpertParallelMoE, expert_range, split_tokens
@@ -436,6 +437,7 @@ def run_ep(args, workload):
     dev = torch.device("cuda", local)
     if "RANK" in os.environ:
         import datetime
+        os.environ.setdefault("NCCL_NVLS_ENABLE", "0")     # plain rings for the few control collectives: no buffer stays bound to a multicast object
         dist.init_process_group("nccl", device_id=dev, timeout=datetime.timedelta(seconds=120))   # a stuck collective is aborted, not waited for
     else:   # plain `python bench.py`: a one-rank group, no collectives are issued
         dist.init_process_group("nccl", init_method="tcp://127.0.0.1:29555", rank=0, world_size=1, device_id=dev)
@@ -447,7 +449,7 @@ def run_ep(args, workload):
     g = torch.Generator(device=dev).manual_seed(0)                      # same gate and tokens on every rank
     ctx.set_gate(0, (torch.randn(E, H, device=dev, generator=g) * 0.02).to(dtype))
     xs_full = {T: torch.randn(T, H, device=dev, generator=g).to(dtype) for T in batches}
-    ep = ExpertParallelMoE(ctx, E, K, H)
+    ep = ExpertParallelMoE(ctx, E, K, H, max_local_tokens=max(batches) // world)
     gl = torch.Generator(device=dev).manual_seed(100 + rank)
     keep = []
     for layer in range(n_layers):
@@ -479,20 +481,6 @@ def run_ep(args, workload):
         l_ = ctx.launches
         eager(T)
         launches_per_T[T] = ctx.launches - l_
-    if args.ep_graph:
-        # One CUDA graph per batch size: router, the NCCL collectives, permute, expert kernels and combine of
-        # every layer replay without a host launch in between (13 launches per layer when eager).
-        for T in batches:
-            for _ in range(2):
-                eager(T)
-        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
-        side = torch.cuda.Stream(device=dev)
-        for T in batches:
-            g_ = torch.cuda.CUDAGraph()
-            with torch.cuda.graph(g_, stream=side, capture_error_mode="thread_local"):
-                out_ = eager(T)
-            graphs[T] = (g_, out_)
-        torch.cuda.synchronize(); dist.barrier(); torch.cuda.synchronize()
     one = (lambda T: graphs[T][0].replay()) if graphs else eager
     def step():
         for T in batches:
@@ -527,18 +515,10 @@ def run_ep(args, workload):
                           "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
                           "config": {"workload": workload, "layer": cfg_name, "hidden": H, "experts": E, "top_k": K, "intermediate": I,
                                      "token_batches": list(batches), "weights": wmode, "parallelism": f"ep{world}: {E // world} experts per GPU, "
-                                     "all-gather dispatch + sum reduce-scatter return over NCCL", "launch": "one CUDA graph replay per batch" if graphs else "eager", "layers": n_layers,
+                                     "peer-store dispatch and return over NVLink (the library's own kernels)", "launch": "one CUDA graph replay per batch" if graphs else "eager", "layers": n_layers,
                                      "gate_bias": "zipf s=1.1 over a seeded permutation" if stack else None},
                           "gpu_launches": args.steps * sum(launches_per_T.values()), "per_T": per_T}), flush=True)
-    if graphs:
-        # Tearing the process group down while captured graphs still hold its collectives blocks forever
-        # (observed: the line above was printed, destroy_process_group never returned): drop the graphs, then leave.
-        for g_, _ in graphs.values():
-            g_.reset()
-        graphs.clear()
-        torch.cuda.synchronize()
-        sys.stdout.flush(); sys.stderr.flush()
-        os._exit(0)
+    ep.close()
     dist.destroy_process_group()
 
 
@@ -553,7 +533,6 @@ def main():
     ap.add_argument("--batches", default=None, help="comma-separated token batches replacing the workload's sweep (profiling runs)")
     ap.add_argument("--ffn-kind", default="auto", choices=["auto", "gemv", "mma"], help="force one expert-FFN kernel family")
     ap.add_argument("--no-graph", action="store_true", help="time eager launches instead of CUDA graph replays")
-    ap.add_argument("--ep-graph", action="store_true", help="expert-parallel workloads: replay one CUDA graph per batch (with its NCCL collectives) instead of eager launches")
     ap.add_argument("--quick", action="store_true", help="timed region only: no e2e, per-T or CPU-baseline legs (for ncu captures)")
     args = ap.parse_args()
     if args.workload in EP_WORKLOADS:

@@ -121,6 +121,18 @@ int b200moe_route_from_logits(b200moe_ctx* ctx, const void* logits, int T, int64
  * logits_out (device).  Lets a caller check moe_layer.py:44 separately from the top-k. */
 int b200moe_last_logits(b200moe_ctx* ctx, int T, float* logits_out, void* stream);
 
+/* Copies the grouping tables the most recent b200moe_forward / b200moe_forward_fused call on this
+ * context built for its T tokens (each destination may be NULL; device or pinned host memory):
+ *   offsets [E+1]      exclusive prefix of the per-expert pair counts, offsets[E] = valid pairs
+ *   sorted_pair [T*K]  pair index t*K+k at each sorted position: expert e owns positions
+ *                      offsets[e] .. offsets[e+1]-1, in row-major (t, k) order - the order in which
+ *                      torch.where(topk_indices == e) lists them (demo/src/model/qwen3_runner.py:305-308)
+ *   inv [T*K]          sorted position of each pair, -1 for an id outside [0,E)
+ *   act_list [E]       experts with work and a usable slot, ascending; n_act [1] = how many
+ * Debug / test read; the reference has no such structure (it re-derives the grouping per expert). */
+int b200moe_last_tables(b200moe_ctx* ctx, int T, int32_t* offsets_out, int32_t* sorted_pair_out, int32_t* inv_out,
+                        int32_t* act_list_out, int32_t* n_act_out, void* stream);
+
 /* Expert execution for a given routing: Qwen3ModelRunner._execute_moe_with_placement
  * (demo/src/model/qwen3_runner.py:269-385) plus, with `residual`, forward_moe's add (:226).
  *   x [T,H]; ids int64 [T,K]; scores [T,K] of scores_dtype (activation dtype or B200MOE_F32);
@@ -143,22 +155,51 @@ int b200moe_forward(b200moe_ctx* ctx, int layer, const void* x, int T, const int
 int b200moe_forward_fused(b200moe_ctx* ctx, int layer, const void* x, int T, const void* residual, void* out,
                           int64_t* ids_out, void* scores_out, int ffn_kind, void* stream);
 
-/* Expert parallelism (no counterpart in the reference, which runs on one GPU; its future-work
- * note is demo/others.md:58-62).  Rank r registers only the experts it owns (contiguous blocks of
- * E/G); the router weight is replicated; each rank routes its own tokens with b200moe_route.
- * Between the two calls below the host layer runs two fixed-size collectives over NCCL:
- * all-gather of (x, ids) before, sum reduce-scatter of the pair-ordered outputs after.
+/* Expert parallelism.  No counterpart in the reference, which runs on one GPU ("expert distribution
+ * across GPUs" is future work there, demo/others.md:58-62); the single-GPU result is the oracle.
  *
- * b200moe_ep_local_experts: expert FFN over ALL ranks' tokens for the experts registered here.
- *   x_all [T_all,H], ids_all int64 [T_all,K] -> y_pairs_out [T_all*K, H] in pair order (row
- *   t*K+k); rows of pairs whose expert lives elsewhere are written as zeros, so summing the
- *   buffers of all ranks reassembles every pair exactly.
- * b200moe_ep_combine: weighted accumulation for this rank's own tokens from their pair rows
- *   y_pairs [T*K, H] (all experts present), same order / rounding rules as b200moe_forward. */
-int b200moe_ep_local_experts(b200moe_ctx* ctx, int layer, const void* x_all, int T_all, const int64_t* ids_all,
-                             void* y_pairs_out, int ffn_kind, void* stream);
-int b200moe_ep_combine(b200moe_ctx* ctx, const void* y_pairs, int T, const int64_t* ids, const void* scores, int scores_dtype,
-                       const int32_t* order, const void* residual, void* out, void* stream);
+ * One process (or context) per GPU; rank r registers only the experts [r*E/G, (r+1)*E/G) it owns, the
+ * router weight is replicated, every rank holds its own slice of the token batch.  Tokens travel to the
+ * experts and results travel back by plain stores into the peers' memory over NVLink, issued by this
+ * library's own kernels - no collective library on the data path, no multicast, no bulk/TMA copy with a
+ * peer address.  Ranks meet through epoch flags in device memory; every wait on a flag is bounded
+ * (about one second unless b200moe_ep_set_wait_ms says otherwise): when a peer never arrives the kernels
+ * finish, b200moe_status reports B200MOE_DEV_WAIT_EXPIRED and the output of that call is not to be used.
+ *
+ * Set-up:
+ *   b200moe_ep_create       allocates this rank's exchange buffer (receive regions for world x
+ *                           max_local_tokens x top_k rows, return rows for its own pairs) and writes a
+ *                           B200MOE_EP_HANDLE_BYTES-byte handle for the other processes (handle_out may
+ *                           be NULL).  The context's max_tokens must be >= world * max_local_tokens.
+ *   b200moe_ep_attach_ipc   handles_all = the handles of all ranks, rank-major (world x 64 bytes, host);
+ *                           the caller exchanges them with whatever it has (torch.distributed, MPI, a file).
+ *   b200moe_ep_attach_local the ranks are contexts of this same process (same GPU, or GPUs with peer access).
+ *   b200moe_ep_detach       unmaps the peers; call it on every rank, after a barrier, before destroy.
+ * Every rank must make the same sequence of layer calls (the flags count them).
+ *
+ * A layer call, b200moe_ep_forward(layer, x_local [T_local,H]) -> out [T_local,H], is three phases that
+ * can also be enqueued one by one (a host that drives several ranks from one thread runs phase by phase):
+ *   b200moe_ep_dispatch  router on the local tokens, then each (token, expert) pair's row is stored into
+ *                        the owner rank's receive region, then count + flag
+ *   b200moe_ep_experts   waits for all sources, groups the received rows by expert (K2), runs the local
+ *                        experts (K3), stores each output row into its source rank's return rows, then flag
+ *   b200moe_ep_combine   waits for all owners, then the weighted accumulation (K4) with the same order /
+ *                        rounding rules as b200moe_forward; residual may be NULL
+ * Results are bit-identical to b200moe_forward_fused on one GPU holding all experts whenever the same
+ * kernel family serves the batch (it is chosen from world * T_local, as on one GPU).
+ * b200moe_ep_last_routing copies the ids / scores the latest dispatch computed for the local tokens. */
+#define B200MOE_EP_HANDLE_BYTES 64
+int b200moe_ep_create(b200moe_ctx* ctx, int world, int rank, int max_local_tokens, void* handle_out);
+int b200moe_ep_attach_ipc(b200moe_ctx* ctx, const void* handles_all);
+int b200moe_ep_attach_local(b200moe_ctx* ctx, b200moe_ctx* const* ranks);
+int b200moe_ep_set_wait_ms(b200moe_ctx* ctx, int milliseconds);
+int b200moe_ep_detach(b200moe_ctx* ctx);
+int b200moe_ep_dispatch(b200moe_ctx* ctx, int layer, const void* x_local, int T_local, void* stream);
+int b200moe_ep_experts(b200moe_ctx* ctx, int layer, int ffn_kind, void* stream);
+int b200moe_ep_combine(b200moe_ctx* ctx, int T_local, const int32_t* order, const void* residual, void* out, void* stream);
+int b200moe_ep_forward(b200moe_ctx* ctx, int layer, const void* x_local, int T_local, const int32_t* order, const void* residual,
+                       void* out, int ffn_kind, void* stream);
+int b200moe_ep_last_routing(b200moe_ctx* ctx, int T_local, int64_t* ids_out, void* scores_out, void* stream);
 
 /* One expert's SwiGLU FFN on n rows: expert_forward_with_weights (demo/src/layers/mlp.py:209-231).
  * Dense weights in the activation dtype; x [n,H] -> out [n,H]. */
@@ -188,10 +229,19 @@ int b200moe_rmsnorm(b200moe_ctx* ctx, const void* x, const void* residual_or_nul
  *   The first call on a device looks up the device address of the array; make that first call
  *   before starting any stream capture.
  *   All calls share the array, which keeps the last call's contents (each call clears the words
- *   that must start at zero): calls that overlap on the GPU race - serialise them. */
+ *   that must start at zero): calls that overlap on the GPU race - serialise them.
+ *   The per-device address table behind the look-up is filled without a lock: two host threads
+ *   making the first call on one device at the same time both store the same address. */
 int b200moe_expert_ffn_noalloc(const void* x, int n, int hidden_size, int intermediate_size, int dtype,
                                const void* gate_proj, const void* up_proj, const void* down_proj, void* out,
                                void* stream);
+
+/* Companion of b200moe_expert_ffn_noalloc, equally allocation-free: waits for `stream`, then copies
+ * the status word the kernels of that entry point keep in the built-in scratch (B200MOE_DEV_* bits of
+ * the most recent call on the current device; each call clears it before its kernels run) to
+ * *device_status_out (host).  Returns B200MOE_E_DEVICE when the word is non-zero - a bounded wait of
+ * a kernel gave up and `out` of that call is not to be trusted.  No counterpart in the reference. */
+int b200moe_expert_ffn_noalloc_status(int* device_status_out, void* stream);
 
 /* Int4 g128 packer / unpacker.  Not in the reference (it has no quantised weights); the format
  * is the one documented at b200moe_set_expert.  w [out,in] in `dtype`; q uint8 [out,in/2];
@@ -219,6 +269,8 @@ int b200moe_status(b200moe_ctx* ctx, int* device_status_out, void* stream);
 #define B200MOE_KERNEL_FFN_GATEUP 2
 #define B200MOE_KERNEL_FFN_DOWN 3
 #define B200MOE_KERNEL_COMBINE 4
+#define B200MOE_KERNEL_EP_DISPATCH 5
+#define B200MOE_KERNEL_EP_RETURN 6
 #define B200MOE_KERNEL_CLASSES 8
 int b200moe_profile(b200moe_ctx* ctx, int enable);
 int b200moe_profile_read(b200moe_ctx* ctx, float* total_ms, int32_t* launches);

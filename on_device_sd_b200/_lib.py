@@ -18,9 +18,10 @@ F32, F16, BF16 = 0, 1, 2
 W_DENSE, W_INT4_G128 = 0, 1
 FFN_AUTO, FFN_GEMV, FFN_MMA = 0, 1, 2
 MAX_EXPERTS, MAX_TOPK = 256, 32
+EP_HANDLE_BYTES = 64
 KERNEL_CLASSES = 8
-KERNEL_NAMES = ("router", "permute", "ffn_gate_up", "ffn_down", "combine")
-ABI_VERSION = 1
+KERNEL_NAMES = ("router", "permute", "ffn_gate_up", "ffn_down", "combine", "ep_dispatch", "ep_return")
+ABI_VERSION = 2
 
 
 class Config(Structure):
@@ -46,11 +47,21 @@ PROTOTYPES = {
     "b200moe_forward": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, POINTER(c_int32),
                                 POINTER(c_int32), c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_forward_fused": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
-    "b200moe_ep_local_experts": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, c_void_p]),
-    "b200moe_ep_combine": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_int, POINTER(c_int32), c_void_p, c_void_p, c_void_p]),
+    "b200moe_ep_create": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p]),
+    "b200moe_ep_attach_ipc": (c_int, [c_void_p, c_void_p]),
+    "b200moe_ep_attach_local": (c_int, [c_void_p, POINTER(c_void_p)]),
+    "b200moe_ep_set_wait_ms": (c_int, [c_void_p, c_int]),
+    "b200moe_ep_detach": (c_int, [c_void_p]),
+    "b200moe_ep_dispatch": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p]),
+    "b200moe_ep_experts": (c_int, [c_void_p, c_int, c_int, c_void_p]),
+    "b200moe_ep_combine": (c_int, [c_void_p, c_int, POINTER(c_int32), c_void_p, c_void_p, c_void_p]),
+    "b200moe_ep_forward": (c_int, [c_void_p, c_int, c_void_p, c_int, POINTER(c_int32), c_void_p, c_void_p, c_int, c_void_p]),
+    "b200moe_ep_last_routing": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_expert_ffn": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_rmsnorm": (c_int, [c_void_p, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_expert_ffn_noalloc": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200moe_expert_ffn_noalloc_status": (c_int, [POINTER(c_int), c_void_p]),
+    "b200moe_last_tables": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_pack_int4": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_unpack_int4": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_profile": (c_int, [c_void_p, c_int]),

@@ -64,6 +64,8 @@ class MoEContext:
         self._gate: Dict[int, Tuple[torch.Tensor, Optional[torch.Tensor]]] = {}
         self._experts: Dict[Tuple[int, int], Tuple[torch.Tensor, ...]] = {}
         self._expert_ptrs: Dict[Tuple[int, int], Tuple[int, ...]] = {}
+        # bumped whenever a registered pointer changes: anything that baked pointers in (a captured CUDA graph) is stale then
+        self.generation = 0
 
     # -- lifetime ---------------------------------------------------------------------------
     def close(self) -> None:
@@ -95,6 +97,7 @@ class MoEContext:
             if bias.shape != (self.E,):
                 raise ValueError(f"gate bias must be [{self.E}]")
         self._gate[layer] = (weight, bias)
+        self.generation += 1
         self._check(self._lib.b200moe_set_gate(self._h, layer, _ptr(weight), _ptr(bias), _stream(self.device)))
 
     def set_expert(self, layer: int, expert: int, params: Dict[str, torch.Tensor]) -> None:
@@ -126,11 +129,13 @@ class MoEContext:
         self._check(self._lib.b200moe_set_expert(self._h, layer, expert, *ptrs))
         self._experts[key] = tensors
         self._expert_ptrs[key] = ptrs
+        self.generation += 1
 
     def clear_expert(self, layer: int, expert: int) -> None:
         self._check(self._lib.b200moe_clear_expert(self._h, layer, expert))
         self._experts.pop((layer, expert), None)
         self._expert_ptrs.pop((layer, expert), None)
+        self.generation += 1
 
     # -- compute ----------------------------------------------------------------------------
     def route(self, layer: int, x2d: torch.Tensor, *, bitmap: Optional[torch.Tensor] = None,
@@ -157,6 +162,14 @@ class MoEContext:
         out = torch.empty(T, self.E, dtype=torch.float32, device=self.device)
         self._check(self._lib.b200moe_last_logits(self._h, T, _ptr(out), _stream(self.device)))
         return out
+
+    def last_tables(self, T: int):
+        """(offsets [E+1], sorted_pair [T*K], inv [T*K], act_list [n_act]) of the latest forward call, as int32 tensors."""
+        i32 = dict(dtype=torch.int32, device=self.device)
+        offsets, sp, inv = torch.empty(self.E + 1, **i32), torch.empty(T * self.K, **i32), torch.empty(T * self.K, **i32)
+        act, n_act = torch.empty(self.E, **i32), torch.empty(1, **i32)
+        self._check(self._lib.b200moe_last_tables(self._h, T, _ptr(offsets), _ptr(sp), _ptr(inv), _ptr(act), _ptr(n_act), _stream(self.device)))
+        return offsets, sp, inv, act[: int(n_act.item())]
 
     def forward(self, layer: int, x2d: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, *,
                 expert_slot: Optional[Sequence[int]] = None, order: Optional[Sequence[int]] = None,
@@ -198,30 +211,74 @@ class MoEContext:
                                                     ffn_kind, _stream(self.device)))
         return (out, ids, scores) if return_routing else out
 
-    def ep_local_experts(self, layer: int, x_all: torch.Tensor, ids_all: torch.Tensor, *, ffn_kind: int = FFN_AUTO,
-                         out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Expert-parallel leg 1: FFN of the experts registered here over all ranks' tokens -> [T_all*K, H] in pair order."""
-        _need_cuda(x_all, "x_all", self.device, self.dtype)
-        _need_cuda(ids_all, "ids_all", self.device, torch.int64)
-        T = x_all.shape[0]
+    # -- expert parallelism (peer-store dispatch / return; include/b200moe.h) -----------------------
+    def ep_create(self, world: int, rank: int, max_local_tokens: int) -> bytes:
+        """Allocates this rank's exchange buffer and returns its 64-byte IPC handle for the other ranks."""
+        buf = ctypes.create_string_buffer(_lib.EP_HANDLE_BYTES)
+        with torch.cuda.device(self.device):
+            self._check(self._lib.b200moe_ep_create(self._h, world, rank, max_local_tokens, buf))
+        self.ep_world, self.ep_rank, self.ep_max_local = world, rank, max_local_tokens
+        return buf.raw
+
+    def ep_attach(self, handles: Sequence[bytes]) -> None:
+        """Maps the other ranks' exchange buffers from their handles (rank-major; this rank's own entry is ignored)."""
+        blob = b"".join(bytes(h) for h in handles)
+        if len(blob) != self.ep_world * _lib.EP_HANDLE_BYTES:
+            raise ValueError(f"expected {self.ep_world} handles of {_lib.EP_HANDLE_BYTES} bytes")
+        with torch.cuda.device(self.device):
+            self._check(self._lib.b200moe_ep_attach_ipc(self._h, blob))
+
+    def ep_attach_local(self, ranks: Sequence["MoEContext"]) -> None:
+        """The ranks are contexts of this process (one GPU emulating several ranks, or peer-accessible GPUs)."""
+        arr = (c_void_p * len(ranks))(*[r._h.value for r in ranks])
+        with torch.cuda.device(self.device):
+            self._check(self._lib.b200moe_ep_attach_local(self._h, arr))
+
+    def ep_set_wait_ms(self, ms: int) -> None:
+        self._check(self._lib.b200moe_ep_set_wait_ms(self._h, ms))
+
+    def ep_detach(self) -> None:
+        self._check(self._lib.b200moe_ep_detach(self._h))
+
+    def ep_dispatch(self, layer: int, x_local: torch.Tensor) -> None:
+        _need_cuda(x_local, "x_local", self.device, self.dtype)
+        if x_local.dim() != 2 or x_local.shape[1] != self.H:
+            raise ValueError(f"x_local must be [T_local,{self.H}]")
+        self._check(self._lib.b200moe_ep_dispatch(self._h, layer, _ptr(x_local), x_local.shape[0], _stream(self.device)))
+
+    def ep_experts(self, layer: int, *, ffn_kind: int = FFN_AUTO) -> None:
+        self._check(self._lib.b200moe_ep_experts(self._h, layer, ffn_kind, _stream(self.device)))
+
+    def ep_combine(self, T_local: int, *, order: Optional[Sequence[int]] = None, residual: Optional[torch.Tensor] = None,
+                   out: Optional[torch.Tensor] = None) -> torch.Tensor:
+        if residual is not None:
+            _need_cuda(residual, "residual", self.device, self.dtype)
         if out is None:
-            out = torch.empty(T * self.K, self.H, dtype=self.dtype, device=self.device)
-        self._check(self._lib.b200moe_ep_local_experts(self._h, layer, _ptr(x_all), T, _ptr(ids_all), _ptr(out), ffn_kind, _stream(self.device)))
+            out = torch.empty(T_local, self.H, dtype=self.dtype, device=self.device)
+        order_arr = (c_int32 * self.E)(*order) if order is not None else None
+        self._check(self._lib.b200moe_ep_combine(self._h, T_local, order_arr, _ptr(residual), _ptr(out), _stream(self.device)))
         return out
 
-    def ep_combine(self, y_pairs: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, *, order: Optional[Sequence[int]] = None,
-                   residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None) -> torch.Tensor:
-        """Expert-parallel leg 2: weighted accumulation of this rank's tokens from their pair rows [T*K, H]."""
-        _need_cuda(y_pairs, "y_pairs", self.device, self.dtype)
-        _need_cuda(ids, "ids", self.device, torch.int64)
-        T = ids.shape[0]
-        scores = scores.contiguous()
+    def ep_forward(self, layer: int, x_local: torch.Tensor, *, order: Optional[Sequence[int]] = None,
+                   residual: Optional[torch.Tensor] = None, out: Optional[torch.Tensor] = None, ffn_kind: int = FFN_AUTO) -> torch.Tensor:
+        """One expert-parallel layer call for this rank's tokens: dispatch, local experts, combine in one enqueue."""
+        _need_cuda(x_local, "x_local", self.device, self.dtype)
+        if x_local.dim() != 2 or x_local.shape[1] != self.H:
+            raise ValueError(f"x_local must be [T_local,{self.H}]")
+        if residual is not None:
+            _need_cuda(residual, "residual", self.device, self.dtype)
         if out is None:
-            out = torch.empty(T, self.H, dtype=self.dtype, device=self.device)
+            out = torch.empty_like(x_local)
         order_arr = (c_int32 * self.E)(*order) if order is not None else None
-        self._check(self._lib.b200moe_ep_combine(self._h, _ptr(y_pairs), T, _ptr(ids), _ptr(scores), dtype_tag(scores.dtype), order_arr,
-                                                 _ptr(residual), _ptr(out), _stream(self.device)))
+        self._check(self._lib.b200moe_ep_forward(self._h, layer, _ptr(x_local), x_local.shape[0], order_arr, _ptr(residual), _ptr(out),
+                                                 ffn_kind, _stream(self.device)))
         return out
+
+    def ep_last_routing(self, T_local: int) -> Tuple[torch.Tensor, torch.Tensor]:
+        ids = torch.empty(T_local, self.K, dtype=torch.int64, device=self.device)
+        scores = torch.empty(T_local, self.K, dtype=self.dtype, device=self.device)
+        self._check(self._lib.b200moe_ep_last_routing(self._h, T_local, _ptr(ids), _ptr(scores), _stream(self.device)))
+        return ids, scores
 
     def expert_ffn(self, x2d: torch.Tensor, gate_proj: torch.Tensor, up_proj: torch.Tensor, down_proj: torch.Tensor) -> torch.Tensor:
         for name, t in (("x", x2d), ("gate_proj", gate_proj), ("up_proj", up_proj), ("down_proj", down_proj)):

@@ -19,6 +19,7 @@
 #include "common.cuh"
 #include "internal.h"
 #include "ffn_gemv.cuh"
+#include "ep.cuh"
 #include "int4_pack.cuh"
 #include "permute.cuh"
 #include "rmsnorm.cuh"
@@ -36,7 +37,6 @@ using namespace b200moe;
 struct b200moe_ctx {
   b200moe_config cfg{};
   int sm_count = 0;
-  int gemv_variant = 0;
   std::string err;
   int64_t launches = 0;
   // registered weights (host mirror) and the device table
@@ -78,6 +78,19 @@ struct b200moe_ctx {
   int* one_act = nullptr;
   int* one_nact = nullptr;
   std::vector<void*> allocs;
+  // expert-parallel exchange (b200moe_ep_*): this rank's exchange buffer, the peers' buffers as this GPU addresses them
+  struct Ep {
+    int world = 0, rank = 0, max_local = 0;
+    bool attached = false;
+    EpGeom geom{};
+    EpPeers peers{};
+    unsigned char* base = nullptr;
+    size_t bytes = 0;
+    unsigned* counters = nullptr;      // [0] epoch, [1] dispatch arrivals, [2] return arrivals
+    long long wait_cycles = 1ll << 31; // about one second
+    std::vector<void*> opened;         // IPC mappings to close
+    int last_T_local = 0;
+  } ep;
   // optional per-kernel timing (b200moe_profile): one event pair per launch, grouped by kernel class
   bool profiling = false;
   struct ProfRec { int cls; cudaEvent_t a, b; };
@@ -130,7 +143,6 @@ int b200moe_fail_global(int code, const char* fmt, ...) {
 
 // Launch with the programmatic-stream-serialization attribute: the kernel may begin while its
 // predecessor in the stream is still running and synchronises on the device (pdl_wait).
-static bool g_use_pdl = getenv("B200MOE_NO_PDL") == nullptr;
 template <typename... KArgs, typename... Args>
 static void launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t s, Args&&... args) {
   cudaLaunchConfig_t cfg = {};
@@ -142,7 +154,7 @@ static void launch_chain(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t
   attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
   attr[0].val.programmaticStreamSerializationAllowed = 1;
   cfg.attrs = attr;
-  cfg.numAttrs = g_use_pdl ? 1 : 0;
+  cfg.numAttrs = 1;
   cudaLaunchKernelEx(&cfg, kernel, std::forward<Args>(args)...);   // errors surface in post_launch
 }
 
@@ -157,7 +169,7 @@ template <typename T> static int dev_alloc(b200moe_ctx* ctx, T** p, size_t count
   return B200MOE_OK;
 }
 
-extern "C" int b200moe_abi_version(void) { return 1; }
+extern "C" int b200moe_abi_version(void) { return 2; }
 
 extern "C" const char* b200moe_last_error(const b200moe_ctx* ctx) { return ctx ? ctx->err.c_str() : g_err.c_str(); }
 
@@ -195,7 +207,6 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
   if (!ctx) return fail(nullptr, B200MOE_E_CUDA, "out of host memory");
   ctx->cfg = *cfg;
   ctx->sm_count = prop.multiProcessorCount;
-  if (const char* v = getenv("B200MOE_GEMV_VARIANT")) ctx->gemv_variant = atoi(v);
   const size_t L = cfg->num_layers, Tm = cfg->max_tokens, eb = elem_bytes(cfg->act_dtype);
   ctx->gate_w.assign(L, nullptr);
   ctx->gate_bias.assign(L, nullptr);
@@ -282,6 +293,7 @@ extern "C" int b200moe_destroy(b200moe_ctx* ctx) {
   if (!ctx) return B200MOE_OK;
   cudaSetDevice(ctx->cfg.device);
   for (auto& r : ctx->prof) { cudaEventDestroy(r.a); cudaEventDestroy(r.b); }
+  for (void* p : ctx->ep.opened) cudaIpcCloseMemHandle(p);
   for (void* p : ctx->allocs) cudaFree(p);
   delete ctx;
   return B200MOE_OK;
@@ -496,6 +508,22 @@ extern "C" int b200moe_last_logits(b200moe_ctx* ctx, int T, float* logits_out, v
   return B200MOE_OK;
 }
 
+extern "C" int b200moe_last_tables(b200moe_ctx* ctx, int T, int32_t* offsets_out, int32_t* sorted_pair_out, int32_t* inv_out,
+                                   int32_t* act_list_out, int32_t* n_act_out, void* stream) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_last_tables: null context");
+  int rc = check_tokens(ctx, T, "b200moe_last_tables");
+  if (rc) return rc;
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t pairs = (size_t)T * ctx->cfg.top_k, E = ctx->cfg.num_experts;
+  if (offsets_out) CUDA_TRY(ctx, cudaMemcpyAsync(offsets_out, ctx->offsets, (E + 1) * sizeof(int), cudaMemcpyDefault, st));
+  if (sorted_pair_out && pairs) CUDA_TRY(ctx, cudaMemcpyAsync(sorted_pair_out, ctx->sorted_pair, pairs * sizeof(int), cudaMemcpyDefault, st));
+  if (inv_out && pairs) CUDA_TRY(ctx, cudaMemcpyAsync(inv_out, ctx->inv, pairs * sizeof(int), cudaMemcpyDefault, st));
+  if (act_list_out) CUDA_TRY(ctx, cudaMemcpyAsync(act_list_out, ctx->act_list, E * sizeof(int), cudaMemcpyDefault, st));
+  if (n_act_out) CUDA_TRY(ctx, cudaMemcpyAsync(n_act_out, ctx->n_act, sizeof(int), cudaMemcpyDefault, st));
+  return B200MOE_OK;
+}
+
 // ------------------------------------------------------------------------------------------
 // expert execution
 // ------------------------------------------------------------------------------------------
@@ -574,11 +602,7 @@ template <typename T, int NT, typename S> static int launch_gemv_pair_shape(b200
 }
 
 template <typename T, int NT> static int launch_gemv_pair(b200moe_ctx* ctx, const FfnParams& p, const SlotTable& st, cudaStream_t s, int which = 3) {
-  switch (ctx->gemv_variant) {   // tuning knob (environment variable B200MOE_GEMV_VARIANT at create time)
-    case 1: return launch_gemv_pair_shape<T, NT, GemvShape<16, 1024, 3>>(ctx, p, st, s, which);
-    case 2: return launch_gemv_pair_shape<T, NT, GemvShape<8, 1024, 6>>(ctx, p, st, s, which);
-    default: return launch_gemv_pair_shape<T, NT, GemvDefault>(ctx, p, st, s, which);
-  }
+  return launch_gemv_pair_shape<T, NT, GemvDefault>(ctx, p, st, s, which);
 }
 
 #ifdef B200MOE_WITH_UMMA
@@ -817,7 +841,7 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   }
   f.n_tokens = T;
   f.n_act_bound = (int)std::min<long long>(E, (long long)T * c.top_k);
-  f.ksplit_ok = scores != nullptr;   // the expert-parallel scatter reads bf16 y
+  f.ksplit_ok = true;
   ctx->last_ksplit = 1;
 #ifdef B200MOE_WITH_UMMA
   if (!ctx->h_tmaps.empty()) {
@@ -829,20 +853,6 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   }
 #endif
   if ((rc = launch_ffn(ctx, f, tab, ffn_kind, st))) return rc;
-
-  if (scores == nullptr) {
-    // expert-parallel leg: no combine here; the expert outputs go back to pair order (t*K + k),
-    // zero rows for pairs served by other ranks, ready for a sum reduce-scatter
-    ScatterParams sp{};
-    sp.y = ctx->y; sp.inv = ctx->inv; sp.ids64 = ids; sp.out = out;
-    sp.npairs = T * c.top_k; sp.H = c.hidden_size; sp.E = E;
-    return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
-      using Tt = decltype(tag);
-      ProfScope prof(ctx, B200MOE_KERNEL_COMBINE, st);
-      launch_chain(scatter_pairs_kernel<Tt>, dim3(sp.npairs), dim3(kCombineThreads), 0, st, sp, tab);
-      return post_launch(ctx, "scatter_pairs_kernel");
-    });
-  }
 
   CombineParams cp{};
   if (ctx->last_ksplit > 1) { cp.ypart = ctx->ypart; cp.y_parts = ctx->last_ksplit; cp.pairs_cap = c.max_tokens * c.top_k; }
@@ -895,35 +905,232 @@ extern "C" int b200moe_forward_fused(b200moe_ctx* ctx, int layer, const void* x,
 }
 
 // ------------------------------------------------------------------------------------------
-// expert-parallel legs
+// expert parallelism: peer-store dispatch / return (ep.cuh)
 // ------------------------------------------------------------------------------------------
-extern "C" int b200moe_ep_local_experts(b200moe_ctx* ctx, int layer, const void* x_all, int T_all, const int64_t* ids_all,
-                                        void* y_pairs_out, int ffn_kind, void* stream) {
-  int rc = check_layer(ctx, layer, "b200moe_ep_local_experts");
+static size_t ep_align(size_t v) { return (v + 255) & ~(size_t)255; }
+
+extern "C" int b200moe_ep_create(b200moe_ctx* ctx, int world, int rank, int max_local_tokens, void* handle_out) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_ep_create: null context");
+  const b200moe_config& c = ctx->cfg;
+  if (ctx->ep.base) return fail(ctx, B200MOE_E_STATE, "b200moe_ep_create: this context already has an exchange buffer");
+  if (world < 1 || world > kEpMaxRanks) return fail(ctx, B200MOE_E_UNSUPPORTED, "b200moe_ep_create: world=%d (1..%d ranks)", world, kEpMaxRanks);
+  if (rank < 0 || rank >= world) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_create: rank %d out of range [0,%d)", rank, world);
+  if (c.num_experts % world) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_create: num_experts=%d is not divisible by world=%d", c.num_experts, world);
+  if (max_local_tokens < 1) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_create: max_local_tokens must be positive");
+  if ((long long)world * max_local_tokens > c.max_tokens)
+    return fail(ctx, B200MOE_E_STATE, "b200moe_ep_create: world*max_local_tokens=%d exceeds the context's max_tokens=%d (the workspace holds every rank's pairs)",
+                world * max_local_tokens, c.max_tokens);
+  CUDA_TRY(ctx, cudaSetDevice(c.device));
+  b200moe_ctx::Ep& ep = ctx->ep;
+  const size_t eb = elem_bytes(c.act_dtype);
+  const int cap = max_local_tokens * c.top_k;
+  EpGeom g{};
+  g.G = world; g.me = rank; g.cap = cap; g.H = c.hidden_size; g.K = c.top_k; g.epr = c.num_experts / world;
+  g.off_meta = kEpHeaderBytes;
+  g.off_x = ep_align(g.off_meta + (size_t)world * cap * sizeof(int2));
+  g.off_ret = ep_align(g.off_x + (size_t)world * cap * c.hidden_size * eb);
+  const size_t bytes = ep_align(g.off_ret + (size_t)cap * c.hidden_size * eb);
+  void* base = nullptr;
+  cudaError_t e = cudaMalloc(&base, bytes);
+  if (e != cudaSuccess) return fail(ctx, B200MOE_E_CUDA, "b200moe_ep_create: cudaMalloc(%zu bytes) failed: %s", bytes, cudaGetErrorString(e));
+  ctx->allocs.push_back(base);
+  int rc = dev_alloc(ctx, &ep.counters, 4);
   if (rc) return rc;
-  if ((rc = check_tokens(ctx, T_all, "b200moe_ep_local_experts"))) return rc;
-  if (T_all == 0) return B200MOE_OK;
-  if (!x_all || !ids_all || !y_pairs_out) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_local_experts: null pointer");
-  if (misaligned(x_all) || misaligned(y_pairs_out)) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_local_experts: x_all and y_pairs_out must be 16-byte aligned");
-  if (ffn_kind < B200MOE_FFN_AUTO || ffn_kind > B200MOE_FFN_MMA) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_local_experts: unknown ffn_kind %d", ffn_kind);
-  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
-  // scores == nullptr selects the scatter-to-pair-order ending of run_experts; experts that are not
-  // registered on this rank are skipped, which is exactly the sharding
-  return run_experts(ctx, layer, x_all, T_all, ids_all, nullptr, ctx->cfg.act_dtype, nullptr, nullptr, nullptr, y_pairs_out, ffn_kind,
-                     reinterpret_cast<cudaStream_t>(stream));
+  CUDA_TRY(ctx, cudaMemset(base, 0, bytes));
+  CUDA_TRY(ctx, cudaMemset(ep.counters, 0, 4 * sizeof(unsigned)));
+  CUDA_TRY(ctx, cudaDeviceSynchronize());
+  if (handle_out) {
+    cudaIpcMemHandle_t h;
+    static_assert(sizeof(cudaIpcMemHandle_t) == B200MOE_EP_HANDLE_BYTES, "handle size");
+    e = cudaIpcGetMemHandle(&h, base);
+    if (e != cudaSuccess) return fail(ctx, B200MOE_E_CUDA, "b200moe_ep_create: cudaIpcGetMemHandle failed: %s", cudaGetErrorString(e));
+    memcpy(handle_out, &h, sizeof h);
+  }
+  ep.world = world; ep.rank = rank; ep.max_local = max_local_tokens; ep.geom = g;
+  ep.base = reinterpret_cast<unsigned char*>(base); ep.bytes = bytes;
+  for (int r = 0; r < kEpMaxRanks; ++r) ep.peers.base[r] = nullptr;
+  ep.peers.base[rank] = ep.base;
+  ep.attached = world == 1;
+  return B200MOE_OK;
 }
 
-extern "C" int b200moe_ep_combine(b200moe_ctx* ctx, const void* y_pairs, int T, const int64_t* ids, const void* scores, int scores_dtype,
-                                  const int32_t* order, const void* residual, void* out, void* stream) {
-  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_ep_combine: null context");
-  int rc = check_tokens(ctx, T, "b200moe_ep_combine");
+extern "C" int b200moe_ep_attach_ipc(b200moe_ctx* ctx, const void* handles_all) {
+  if (!ctx || !handles_all) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_attach_ipc: null argument");
+  b200moe_ctx::Ep& ep = ctx->ep;
+  if (!ep.base) return fail(ctx, B200MOE_E_STATE, "b200moe_ep_attach_ipc: call b200moe_ep_create first");
+  if (ep.attached && ep.world > 1) return fail(ctx, B200MOE_E_STATE, "b200moe_ep_attach_ipc: already attached");
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  const unsigned char* hb = reinterpret_cast<const unsigned char*>(handles_all);
+  for (int r = 0; r < ep.world; ++r) {
+    if (r == ep.rank) continue;
+    cudaIpcMemHandle_t h;
+    memcpy(&h, hb + (size_t)r * B200MOE_EP_HANDLE_BYTES, sizeof h);
+    void* ptr = nullptr;
+    cudaError_t e = cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess);
+    if (e != cudaSuccess) return fail(ctx, B200MOE_E_CUDA, "b200moe_ep_attach_ipc: cudaIpcOpenMemHandle for rank %d failed: %s", r, cudaGetErrorString(e));
+    ep.opened.push_back(ptr);
+    ep.peers.base[r] = reinterpret_cast<unsigned char*>(ptr);
+  }
+  ep.attached = true;
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_ep_attach_local(b200moe_ctx* ctx, b200moe_ctx* const* ranks) {
+  if (!ctx || !ranks) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_attach_local: null argument");
+  b200moe_ctx::Ep& ep = ctx->ep;
+  if (!ep.base) return fail(ctx, B200MOE_E_STATE, "b200moe_ep_attach_local: call b200moe_ep_create first");
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  for (int r = 0; r < ep.world; ++r) {
+    if (r == ep.rank) continue;
+    const b200moe_ctx* o = ranks[r];
+    if (!o || !o->ep.base) return fail(ctx, B200MOE_E_STATE, "b200moe_ep_attach_local: rank %d has no exchange buffer", r);
+    if (o->ep.world != ep.world || o->ep.rank != r || o->ep.bytes != ep.bytes)
+      return fail(ctx, B200MOE_E_ARG, "b200moe_ep_attach_local: rank %d was created with a different geometry", r);
+    if (o->cfg.device != ctx->cfg.device) {
+      cudaError_t e = cudaDeviceEnablePeerAccess(o->cfg.device, 0);
+      if (e == cudaErrorPeerAccessAlreadyEnabled) { cudaGetLastError(); e = cudaSuccess; }
+      if (e != cudaSuccess) return fail(ctx, B200MOE_E_CUDA, "b200moe_ep_attach_local: no peer access from device %d to %d: %s", ctx->cfg.device, o->cfg.device, cudaGetErrorString(e));
+    }
+    ep.peers.base[r] = o->ep.base;
+  }
+  ep.attached = true;
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_ep_set_wait_ms(b200moe_ctx* ctx, int milliseconds) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_ep_set_wait_ms: null context");
+  if (milliseconds < 1 || milliseconds > 2000) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_set_wait_ms: 1..2000 ms");
+  int khz = 0;
+  if (cudaDeviceGetAttribute(&khz, cudaDevAttrClockRate, ctx->cfg.device) != cudaSuccess || khz <= 0) khz = 1965000;
+  ctx->ep.wait_cycles = (long long)khz * milliseconds;
+  return B200MOE_OK;
+}
+
+extern "C" int b200moe_ep_detach(b200moe_ctx* ctx) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_ep_detach: null context");
+  cudaSetDevice(ctx->cfg.device);
+  for (void* p : ctx->ep.opened) cudaIpcCloseMemHandle(p);
+  ctx->ep.opened.clear();
+  for (int r = 0; r < kEpMaxRanks; ++r)
+    if (r != ctx->ep.rank) ctx->ep.peers.base[r] = nullptr;
+  ctx->ep.attached = ctx->ep.world == 1;
+  return B200MOE_OK;
+}
+
+static int ep_ready(b200moe_ctx* ctx, const char* who) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "%s: null context", who);
+  if (!ctx->ep.base) return fail(ctx, B200MOE_E_STATE, "%s: no exchange buffer (b200moe_ep_create)", who);
+  if (!ctx->ep.attached) return fail(ctx, B200MOE_E_STATE, "%s: peers not attached (b200moe_ep_attach_ipc / _local)", who);
+  return B200MOE_OK;
+}
+
+// phase 1: route this rank's tokens, then store every (token, expert) pair's row into its owner's receive buffer
+extern "C" int b200moe_ep_dispatch(b200moe_ctx* ctx, int layer, const void* x_local, int T_local, void* stream) {
+  int rc = ep_ready(ctx, "b200moe_ep_dispatch");
   if (rc) return rc;
-  if (T == 0) return B200MOE_OK;
-  if (!y_pairs || !ids || !scores || !out) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_combine: null pointer");
-  if (misaligned(y_pairs) || misaligned(out) || (residual && misaligned(residual)))
-    return fail(ctx, B200MOE_E_ARG, "b200moe_ep_combine: y_pairs, out and residual must be 16-byte aligned");
+  if ((rc = check_layer(ctx, layer, "b200moe_ep_dispatch"))) return rc;
+  b200moe_ctx::Ep& ep = ctx->ep;
   const b200moe_config& c = ctx->cfg;
-  if (scores_dtype != c.act_dtype && scores_dtype != B200MOE_F32) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_combine: scores must be in the activation dtype or fp32");
+  if (T_local < 0 || T_local > ep.max_local) return fail(ctx, B200MOE_E_STATE, "b200moe_ep_dispatch: T_local=%d outside [0, max_local_tokens=%d]", T_local, ep.max_local);
+  if (T_local > 0 && (!x_local || misaligned(x_local))) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_dispatch: x_local must be a 16-byte aligned device pointer");
+  if (!ctx->gate_w[layer]) return fail(ctx, B200MOE_E_STATE, "b200moe_ep_dispatch: no gate weight registered for layer %d", layer);
+  CUDA_TRY(ctx, cudaSetDevice(c.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (T_local > 0 && (rc = launch_router(ctx, layer, x_local, nullptr, T_local, ctx->ids64, ctx->scores, nullptr, st))) return rc;
+  EpDispatchParams dp{};
+  dp.x = x_local; dp.ids = ctx->ids64; dp.T_local = T_local; dp.E = c.num_experts; dp.g = ep.geom;
+  dp.epoch = ep.counters; dp.done = ep.counters + 1; dp.status = ctx->status;
+  const int pairs = T_local * c.top_k;
+  const int grid = std::max(1, (pairs + kEpPairsPerCta - 1) / kEpPairsPerCta);
+  ep.last_T_local = T_local;
+  return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
+    using Tt = decltype(tag);
+    ProfScope prof(ctx, B200MOE_KERNEL_EP_DISPATCH, st);
+    launch_chain(ep_dispatch_kernel<Tt>, dim3(grid), dim3(kEpThreads), 0, st, dp, ep.peers);
+    return post_launch(ctx, "ep_dispatch_kernel");
+  });
+}
+
+// phase 2: wait for every source's rows, group them by expert, run the local experts, store every output row into its source's return buffer
+extern "C" int b200moe_ep_experts(b200moe_ctx* ctx, int layer, int ffn_kind, void* stream) {
+  int rc = ep_ready(ctx, "b200moe_ep_experts");
+  if (rc) return rc;
+  if ((rc = check_layer(ctx, layer, "b200moe_ep_experts"))) return rc;
+  if (ffn_kind < B200MOE_FFN_AUTO || ffn_kind > B200MOE_FFN_MMA) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_experts: unknown ffn_kind %d", ffn_kind);
+  b200moe_ctx::Ep& ep = ctx->ep;
+  const b200moe_config& c = ctx->cfg;
+  const int E = c.num_experts;
+  CUDA_TRY(ctx, cudaSetDevice(c.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  SlotTable tab;
+  for (int e = 0; e < kMaxExperts; ++e) { tab.slot[e] = -1; tab.rank[e] = (uint8_t)(e & 255); }
+  for (int e = 0; e < E; ++e) tab.slot[e] = (int16_t)(ctx->registered[(size_t)layer * E + e] ? e : -1);
+  if ((rc = upload_layer_table(ctx, layer, st))) return rc;
+  const EpGeom& g = ep.geom;
+  const int rows = g.G * g.cap;                      // every row of the receive buffer is a "pair" with K = 1
+  const EpHeader* hdr = reinterpret_cast<const EpHeader*>(ep.base);
+  PermuteParams pp{};
+  pp.ids64 = nullptr; pp.T = rows; pp.K = 1; pp.E = E;
+  pp.offsets = ctx->offsets; pp.sorted_pair = ctx->sorted_pair; pp.inv = ctx->inv;
+  pp.act_list = ctx->act_list; pp.n_act = ctx->n_act; pp.status = ctx->status;
+  pp.ep_meta = reinterpret_cast<const int2*>(ep.base + g.off_meta);
+  pp.ep_count = hdr->disp_count; pp.ep_flags = hdr->disp_flag; pp.ep_epoch = ep.counters;
+  pp.ep_G = g.G; pp.ep_cap = g.cap; pp.ep_wait_cycles = ep.wait_cycles;
+  const int pthreads = std::min(kPermuteMaxThreads, std::max(256, (rows + 31) / 32 * 32));
+  const size_t smem = (size_t)((pthreads / 32) * E + E) * sizeof(int);
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_PERMUTE, st);
+    launch_chain(permute_kernel, dim3(1), dim3(pthreads), smem, st, pp, tab);
+  }
+  if ((rc = post_launch(ctx, "permute_kernel"))) return rc;
+
+  FfnLaunch f{};
+  f.experts = ctx->d_experts + (size_t)layer * E;
+  f.offsets = ctx->offsets; f.sorted_pair = ctx->sorted_pair; f.act_list = ctx->act_list; f.n_act = ctx->n_act;
+  f.x = ep.base + g.off_x; f.h = ctx->h; f.y = ctx->y; f.K = 1;
+  {
+    // same token-tile rule as on one GPU, from the whole batch (all ranks' tokens), so that the same
+    // kernel instance - and with it the same summation order - serves an expert wherever it lives
+    const long long T_all = (long long)g.G * std::max(1, ep.last_T_local);
+    const long long n_mean = (T_all * c.top_k + E - 1) / E;
+    f.max_n = (int)std::min<long long>(T_all, std::max<long long>(16, 4 * n_mean));
+  }
+  f.n_tokens = rows;
+  f.n_act_bound = std::min(g.epr, rows);
+  f.ksplit_ok = false;                               // the return kernel ships y rows in the model dtype
+  ctx->last_ksplit = 1;
+#ifdef B200MOE_WITH_UMMA
+  if (!ctx->h_tmaps.empty()) {
+    bool all_ok = true;
+    for (int e = 0; e < E; ++e)
+      if (tab.slot[e] >= 0 && !ctx->tmap_ok[(size_t)layer * E + tab.slot[e]]) all_ok = false;
+    if (all_ok) f.tmaps = ctx->d_tmaps + (size_t)layer * E * 3;
+    if (all_ok && ctx->d_tmaps2) f.tmaps2 = ctx->d_tmaps2 + (size_t)layer * E * 3;
+  }
+#endif
+  if ((rc = launch_ffn(ctx, f, tab, ffn_kind, st))) return rc;
+
+  EpReturnParams rp{};
+  rp.y = ctx->y; rp.offsets = ctx->offsets; rp.sorted_pair = ctx->sorted_pair; rp.E = E; rp.g = g;
+  rp.epoch = ep.counters; rp.done = ep.counters + 2; rp.status = ctx->status;
+  const int grid = std::max(1, std::min(rows, 4 * ctx->sm_count));
+  return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
+    using Tt = decltype(tag);
+    ProfScope prof(ctx, B200MOE_KERNEL_EP_RETURN, st);
+    launch_chain(ep_return_kernel<Tt>, dim3(grid), dim3(kEpThreads), 0, st, rp, ep.peers, tab);
+    return post_launch(ctx, "ep_return_kernel");
+  });
+}
+
+// phase 3: wait for every owner's rows, then the weighted accumulation of this rank's own tokens
+extern "C" int b200moe_ep_combine(b200moe_ctx* ctx, int T_local, const int32_t* order, const void* residual, void* out, void* stream) {
+  int rc = ep_ready(ctx, "b200moe_ep_combine");
+  if (rc) return rc;
+  b200moe_ctx::Ep& ep = ctx->ep;
+  const b200moe_config& c = ctx->cfg;
+  if (T_local != ep.last_T_local) return fail(ctx, B200MOE_E_STATE, "b200moe_ep_combine: T_local=%d but the matching dispatch had %d tokens", T_local, ep.last_T_local);
+  if (T_local == 0) return B200MOE_OK;
+  if (!out || misaligned(out) || (residual && misaligned(residual))) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_combine: out and residual must be 16-byte aligned device pointers");
   CUDA_TRY(ctx, cudaSetDevice(c.device));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   SlotTable tab;
@@ -933,17 +1140,38 @@ extern "C" int b200moe_ep_combine(b200moe_ctx* ctx, const void* y_pairs, int T, 
       if (order[e] < 0 || order[e] > 255) return fail(ctx, B200MOE_E_ARG, "order[%d]=%d out of range [0,255]", e, order[e]);
       tab.rank[e] = (uint8_t)order[e];
     }
+  const EpHeader* hdr = reinterpret_cast<const EpHeader*>(ep.base);
   CombineParams cp{};
-  cp.y = y_pairs; cp.inv = ctx->one_sorted;   // identity: pair p lives in row p
-  cp.ids64 = ids; cp.scores = scores;
-  cp.scores_f32 = (scores_dtype == B200MOE_F32 && c.act_dtype != B200MOE_F32) ? 1 : 0;
-  cp.residual = residual; cp.out = out; cp.T = T; cp.H = c.hidden_size; cp.K = c.top_k; cp.E = c.num_experts;
+  cp.y = ep.base + ep.geom.off_ret; cp.inv = ctx->one_sorted;   // identity: pair p lives in row p of the return buffer
+  cp.ids64 = ctx->ids64; cp.scores = ctx->scores; cp.scores_f32 = 0;
+  cp.residual = residual; cp.out = out; cp.T = T_local; cp.H = c.hidden_size; cp.K = c.top_k; cp.E = c.num_experts;
+  cp.wait_flags = hdr->ret_flag; cp.epoch = ep.counters; cp.n_wait = ep.geom.G; cp.wait_cycles = ep.wait_cycles; cp.status = ctx->status;
   return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
     using Tt = decltype(tag);
     ProfScope prof(ctx, B200MOE_KERNEL_COMBINE, st);
-    launch_chain(combine_kernel<Tt>, dim3(T), dim3(kCombineThreads), 0, st, cp, tab);
+    launch_chain(combine_kernel<Tt>, dim3(T_local), dim3(kCombineThreads), 0, st, cp, tab);
     return post_launch(ctx, "combine_kernel");
   });
+}
+
+extern "C" int b200moe_ep_forward(b200moe_ctx* ctx, int layer, const void* x_local, int T_local, const int32_t* order, const void* residual,
+                                  void* out, int ffn_kind, void* stream) {
+  int rc = b200moe_ep_dispatch(ctx, layer, x_local, T_local, stream);
+  if (rc) return rc;
+  if ((rc = b200moe_ep_experts(ctx, layer, ffn_kind, stream))) return rc;
+  return b200moe_ep_combine(ctx, T_local, order, residual, out, stream);
+}
+
+extern "C" int b200moe_ep_last_routing(b200moe_ctx* ctx, int T_local, int64_t* ids_out, void* scores_out, void* stream) {
+  int rc = ep_ready(ctx, "b200moe_ep_last_routing");
+  if (rc) return rc;
+  if (T_local < 0 || T_local > ctx->ep.max_local) return fail(ctx, B200MOE_E_ARG, "b200moe_ep_last_routing: T_local out of range");
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const size_t n = (size_t)T_local * ctx->cfg.top_k;
+  if (ids_out && n) CUDA_TRY(ctx, cudaMemcpyAsync(ids_out, ctx->ids64, n * sizeof(int64_t), cudaMemcpyDefault, st));
+  if (scores_out && n) CUDA_TRY(ctx, cudaMemcpyAsync(scores_out, ctx->scores, n * elem_bytes(ctx->cfg.act_dtype), cudaMemcpyDefault, st));
+  return B200MOE_OK;
 }
 
 extern "C" int b200moe_rmsnorm(b200moe_ctx* ctx, const void* x, const void* residual_or_null, const void* weight, float eps, int T,

@@ -59,6 +59,9 @@ template <> struct Chunk<float> {
     if (kStream) { a = ldg_stream(p); b = ldg_stream(p + 4); }
     else { a = ldg_cached(p); b = ldg_cached(p + 4); }
   }
+  __device__ __forceinline__ void load_cg(const float* p) {     // through L2 only: data another GPU may have just written
+    a = __ldcg(reinterpret_cast<const uint4*>(p)); b = __ldcg(reinterpret_cast<const uint4*>(p) + 1);
+  }
   __device__ __forceinline__ void from_smem(const void* p) {   // 32 bytes
     a = reinterpret_cast<const uint4*>(p)[0];
     b = reinterpret_cast<const uint4*>(p)[1];
@@ -75,6 +78,7 @@ template <> struct Chunk<__nv_bfloat16> {
   template <bool kStream> __device__ __forceinline__ void load(const __nv_bfloat16* p) {
     a = kStream ? ldg_stream(p) : ldg_cached(p);
   }
+  __device__ __forceinline__ void load_cg(const void* p) { a = __ldcg(reinterpret_cast<const uint4*>(p)); }
   __device__ __forceinline__ void from_smem(const void* p) { a = *reinterpret_cast<const uint4*>(p); }
   __device__ __forceinline__ void zero() { a = make_uint4(0, 0, 0, 0); }
   __device__ __forceinline__ void unpack(float (&f)[8]) const {
@@ -91,6 +95,7 @@ template <> struct Chunk<__half> {
   template <bool kStream> __device__ __forceinline__ void load(const __half* p) {
     a = kStream ? ldg_stream(p) : ldg_cached(p);
   }
+  __device__ __forceinline__ void load_cg(const void* p) { a = __ldcg(reinterpret_cast<const uint4*>(p)); }
   __device__ __forceinline__ void from_smem(const void* p) { a = *reinterpret_cast<const uint4*>(p); }
   __device__ __forceinline__ void zero() { a = make_uint4(0, 0, 0, 0); }
   __device__ __forceinline__ void unpack(float (&f)[8]) const {
@@ -123,6 +128,31 @@ __device__ __forceinline__ float silu_f32(float g) { return g / (1.0f + expf(-g)
 // chain, any earlier kernel) produces or still reads.  pdl_trigger() lets the successor launch.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// ---------------------------------------------------------------------------------------------
+// Flags that another GPU writes (expert-parallel exchange, ep.cuh): system-scope release / acquire.
+// ---------------------------------------------------------------------------------------------
+__device__ __forceinline__ unsigned ld_acquire_sys(const unsigned* p) {
+  unsigned v;
+  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+  return v;
+}
+__device__ __forceinline__ void st_release_sys(unsigned* p, unsigned v) {
+  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+}
+__device__ __forceinline__ uint4 ld_cg16(const void* p) { return __ldcg(reinterpret_cast<const uint4*>(p)); }
+
+// Waits until the flag has reached `epoch` (signed distance, so the counter may wrap), for at most
+// `limit` cycles.  The flag lives in this GPU's memory; a peer writes it.
+__device__ __forceinline__ bool ep_wait_flag(const unsigned* flag, unsigned epoch, long long limit) {
+  if ((int)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+  const long long t0 = clock64();
+  for (;;) {
+    __nanosleep(100);
+    if ((int)(ld_acquire_sys(flag) - epoch) >= 0) return true;
+    if (clock64() - t0 > limit) return false;
+  }
+}
 
 // Device status word bits (mirrors B200MOE_DEV_* of the public header).
 constexpr int kDevBadExpertId = 1;

@@ -1,0 +1,189 @@
+// Expert-parallel dispatch and return over NVLink peer memory (no counterpart in the reference,
+// which runs on one GPU; "expert distribution across GPUs" is future work there, demo/others.md:58-62).
+//
+// Rank r owns experts [r*E/G, (r+1)*E/G).  Every rank holds one "exchange buffer" of identical
+// layout that its peers can write (mapped through CUDA IPC handles, or plain pointers inside one process):
+//
+//   header     disp_flag[G]   epoch of the latest dispatch by source rank s   (written by s)
+//              disp_count[G]  rows that source rank s sent in that dispatch   (written by s)
+//              ret_flag[G]    epoch of the latest return by owner rank o      (written by o)
+//   recv_meta  int2 [G][cap]  (expert id, pair index t_local*K+k on the source) of every received row
+//   recv_x     T    [G][cap][H]   the token row of every received (token, expert) pair, one region per source
+//   ret_y      T    [cap][H]      expert outputs of this rank's own pairs, in pair order, written by the owners
+//
+// One layer forward on every rank:
+//   route (local tokens) -> ep_dispatch_kernel: each pair's token row goes straight into the owner's
+//   recv_x region for this source, then count + flag -> permute (waits for all G flags, groups the received
+//   rows by expert) -> expert FFN over the LOCAL receive buffer -> ep_return_kernel: each output row goes
+//   straight into its source's ret_y, then flag -> combine on the source (waits for all G flags).
+//
+// Only plain st.global / ld.global touch peer memory: no TMA, no bulk copy, no multicast, no library
+// kernel ever sees a peer address.  Flags are epochs (one per layer call, kept on the device so a call
+// sequence can be replayed), written with st.release.sys after a system-scope fence and polled with
+// ld.acquire.sys; every poll loop gives up after a cycle budget, sets B200MOE_DEV_WAIT_EXPIRED and
+// lets the kernel finish, so nothing can hang.  A rank starts the dispatch of call n+1 only after it
+// has seen every owner's return flag of call n, and an owner raises that flag after its expert
+// kernels are done with the receive buffer, so one buffer set is enough (no double buffering).
+#pragma once
+#include "common.cuh"
+#include "permute.cuh"
+
+namespace b200moe {
+
+constexpr int kEpMaxRanks = 8;
+constexpr int kEpHeaderBytes = 256;
+constexpr int kEpThreads = 256;
+constexpr int kEpPairsPerCta = 4;
+
+struct EpHeader {
+  unsigned disp_flag[kEpMaxRanks];
+  int disp_count[kEpMaxRanks];
+  unsigned ret_flag[kEpMaxRanks];
+};
+static_assert(sizeof(EpHeader) <= kEpHeaderBytes, "header");
+
+struct EpPeers { unsigned char* base[kEpMaxRanks]; };   // exchange buffer of every rank as addressed from this GPU
+
+struct EpGeom {
+  int G, me, cap, H, K, epr;                 // ranks, this rank, rows per (destination, source) region, hidden, top-k, experts per rank
+  unsigned long long off_meta, off_x, off_ret;
+};
+
+struct EpDispatchParams {
+  const void* x;          // [T_local, H]
+  const int64_t* ids;     // [T_local, K] from the router
+  int T_local, E;
+  EpGeom g;
+  unsigned* epoch;        // this rank's call counter (device)
+  unsigned* done;         // CTA arrival counter, zero between launches
+  int* status;
+};
+
+// grid = ceil(pairs / kEpPairsPerCta) (at least 1).  Pair p = t*K+k goes to rank d = ids[p] / epr, row
+// "number of earlier pairs with the same destination" of region [d][me]: every source fills its region
+// densely and in pair order, so the layout does not depend on timing.
+template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(EpDispatchParams p, EpPeers peers) {
+  __shared__ int s_cnt[kEpMaxRanks];
+  __shared__ int s_dst[kEpPairsPerCta], s_pos[kEpPairsPerCta], s_exp[kEpPairsPerCta];
+  __shared__ int s_last;
+  const EpGeom& g = p.g;
+  const int npairs = p.T_local * g.K;
+  const int p0 = blockIdx.x * kEpPairsPerCta;
+  if (threadIdx.x < kEpMaxRanks) s_cnt[threadIdx.x] = 0;
+  pdl_wait();        // ids come from the router launched just before; the previous call's combine is complete too
+  pdl_trigger();
+  __syncthreads();
+  for (int i = threadIdx.x; i < min(p0, npairs); i += kEpThreads) {
+    const long long e = p.ids[i];
+    if (e >= 0 && e < p.E) atomicAdd(&s_cnt[(int)e / g.epr], 1);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < kEpPairsPerCta; ++i) {
+      const int pr = p0 + i;
+      s_dst[i] = -1;
+      if (pr < npairs) {
+        const long long e = p.ids[pr];
+        if (e >= 0 && e < p.E) {
+          const int d = (int)e / g.epr;
+          s_dst[i] = d; s_pos[i] = s_cnt[d]++; s_exp[i] = (int)e;
+        } else {
+          atomicOr(p.status, kDevBadExpertId);
+        }
+      }
+    }
+  }
+  __syncthreads();
+  const int nch = g.H / 8;
+  constexpr int CB = 8 * (int)sizeof(T);
+  for (int i = 0; i < kEpPairsPerCta; ++i) {
+    const int d = s_dst[i];
+    if (d < 0 || s_pos[i] >= g.cap) continue;
+    const int pr = p0 + i;
+    const size_t row = (size_t)g.me * g.cap + s_pos[i];
+    unsigned char* dst = peers.base[d] + g.off_x + row * (size_t)g.H * sizeof(T);
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.x) + (size_t)(pr / g.K) * g.H * sizeof(T);
+    for (int c = threadIdx.x; c < nch; c += kEpThreads) {
+      if (sizeof(T) == 2) {
+        *reinterpret_cast<uint4*>(dst + (size_t)c * CB) = ldg_cached(src + (size_t)c * CB);
+      } else {
+        *reinterpret_cast<uint4*>(dst + (size_t)c * CB) = ldg_cached(src + (size_t)c * CB);
+        *reinterpret_cast<uint4*>(dst + (size_t)c * CB + 16) = ldg_cached(src + (size_t)c * CB + 16);
+      }
+    }
+    if (threadIdx.x == 0) reinterpret_cast<int2*>(peers.base[d] + g.off_meta)[row] = make_int2(s_exp[i], pr);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(p.done, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (!s_last) return;
+  // last CTA: every row of this rank has been written and fenced; publish counts, then the flags
+  __threadfence_system();
+  if (threadIdx.x < kEpMaxRanks) s_cnt[threadIdx.x] = 0;
+  __syncthreads();
+  for (int i = threadIdx.x; i < npairs; i += kEpThreads) {
+    const long long e = p.ids[i];
+    if (e >= 0 && e < p.E) atomicAdd(&s_cnt[(int)e / g.epr], 1);
+  }
+  __syncthreads();
+  const unsigned epoch = *p.epoch + 1u;
+  if (threadIdx.x < g.G) {
+    EpHeader* h = reinterpret_cast<EpHeader*>(peers.base[threadIdx.x]);
+    h->disp_count[g.me] = min(s_cnt[threadIdx.x], g.cap);
+    __threadfence_system();
+    st_release_sys(&h->disp_flag[g.me], epoch);
+  }
+  __syncthreads();
+  if (threadIdx.x == 0) { *p.epoch = epoch; *p.done = 0u; }
+}
+
+struct EpReturnParams {
+  const void* y;            // [rows, H] expert outputs in sorted order
+  const int* offsets;       // [E+1]
+  const int* sorted_pair;   // sorted position -> row of the receive buffer (s*cap + j)
+  int E;
+  EpGeom g;
+  const unsigned* epoch;
+  unsigned* done;
+  int* status;
+};
+
+// One CTA per sorted row (grid-stride).  Rows of experts this rank does not serve are returned as zeros,
+// so that every pair row of every source is rewritten in every call.
+template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_return_kernel(EpReturnParams p, EpPeers peers, SlotTable st) {
+  __shared__ int s_last;
+  const EpGeom& g = p.g;
+  pdl_wait();        // y comes from the down projection launched just before
+  pdl_trigger();
+  const int total = min(p.offsets[p.E], g.G * g.cap);
+  const int2* meta = reinterpret_cast<const int2*>(peers.base[g.me] + g.off_meta);
+  const int nch = g.H / 8;
+  constexpr int CB = 8 * (int)sizeof(T);
+  for (int pos = blockIdx.x; pos < total; pos += gridDim.x) {
+    const int row = p.sorted_pair[pos];
+    if (row < 0 || row >= g.G * g.cap) { if (threadIdx.x == 0) atomicOr(p.status, kDevBadOffsets); continue; }
+    const int s = row / g.cap;
+    const int2 m = __ldcg(meta + row);
+    if (m.y < 0 || m.y >= g.cap) { if (threadIdx.x == 0) atomicOr(p.status, kDevBadOffsets); continue; }
+    const bool served = m.x >= 0 && m.x < p.E && st.slot[m.x] >= 0;
+    unsigned char* dst = peers.base[s] + g.off_ret + (size_t)m.y * g.H * sizeof(T);
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.y) + (size_t)pos * g.H * sizeof(T);
+    for (int c = threadIdx.x; c < nch; c += kEpThreads) {
+      const uint4 z = make_uint4(0, 0, 0, 0);
+      *reinterpret_cast<uint4*>(dst + (size_t)c * CB) = served ? ld_cg16(src + (size_t)c * CB) : z;
+      if (sizeof(T) == 4) *reinterpret_cast<uint4*>(dst + (size_t)c * CB + 16) = served ? ld_cg16(src + (size_t)c * CB + 16) : z;
+    }
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) s_last = (atomicAdd(p.done, 1u) == gridDim.x - 1);
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence_system();
+  const unsigned epoch = *p.epoch;
+  if (threadIdx.x < g.G) st_release_sys(&reinterpret_cast<EpHeader*>(peers.base[threadIdx.x])->ret_flag[g.me], epoch);
+  if (threadIdx.x == 0) *p.done = 0u;
+}
+
+}  // namespace b200moe

@@ -58,7 +58,9 @@ __global__ void noalloc_setup_kernel(const void* gate, const void* up, const voi
 }
 
 constexpr int kMaxDevices = 64;
-void* g_scratch_addr[kMaxDevices];   // per device, filled by the first call on that device
+// Per device, filled by the first call on that device.  No lock: concurrent first calls on one
+// device resolve the same symbol and store the same pointer, so the race is benign.
+void* g_scratch_addr[kMaxDevices];
 
 using Shape = GemvShape<8, 2048, 3>;
 
@@ -143,4 +145,23 @@ extern "C" int b200moe_expert_ffn_noalloc(const void* x, int n, int hidden_size,
     case B200MOE_F16: return run<__half>(p, tab, &sc->status, n, sms, st);
     default: return run<__nv_bfloat16>(p, tab, &sc->status, n, sms, st);
   }
+}
+
+extern "C" int b200moe_expert_ffn_noalloc_status(int* device_status_out, void* stream) {
+  if (!device_status_out) return b200moe_fail_global(B200MOE_E_ARG, "b200moe_expert_ffn_noalloc_status: null argument");
+  int dev = -1;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return b200moe_fail_global(B200MOE_E_CUDA, "b200moe_expert_ffn_noalloc_status: no CUDA device: %s", cudaGetErrorString(e));
+  if (dev < 0 || dev >= kMaxDevices) return b200moe_fail_global(B200MOE_E_UNSUPPORTED, "b200moe_expert_ffn_noalloc_status: device ordinal %d not supported", dev);
+  *device_status_out = 0;
+  if (g_scratch_addr[dev] == nullptr) return B200MOE_OK;   // no call has run on this device yet
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const NoAllocScratch* sc = reinterpret_cast<const NoAllocScratch*>(g_scratch_addr[dev]);   // device address
+  int v = 0;
+  e = cudaMemcpyAsync(&v, &sc->status, sizeof v, cudaMemcpyDeviceToHost, st);
+  if (e == cudaSuccess) e = cudaStreamSynchronize(st);
+  if (e != cudaSuccess) return b200moe_fail_global(B200MOE_E_CUDA, "b200moe_expert_ffn_noalloc_status: %s", cudaGetErrorString(e));
+  *device_status_out = v;
+  if (v) return b200moe_fail_global(B200MOE_E_DEVICE, "b200moe_expert_ffn_noalloc: device status word = %d (a bounded wait gave up; the output is incomplete)", v);
+  return B200MOE_OK;
 }

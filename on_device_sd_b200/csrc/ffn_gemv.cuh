@@ -227,6 +227,11 @@ __global__ void __launch_bounds__(S::THREADS, 1) ffn_gemv_kernel(FfnParams p, Sl
       }
     }
   }
+  if (dead) {
+    // A wait ran out.  Copies issued earlier may still be in flight towards this warp's ring: give each
+    // of them a short, bounded chance to land before the shared memory can pass to another CTA.
+    for (int i = consumed; i < issued; ++i) mbar_wait_brief(&full[i % STAGES], (uint32_t)(i / STAGES) & 1u);
+  }
 }
 
 // ---------------------------------------------------------------------------------------------
@@ -245,6 +250,14 @@ struct CombineParams {
   const void* residual; // [T,H] or null
   void* out;            // [T,H]
   int T, H, K, E;
+  // Expert-parallel mode (wait_flags != null): y is the return buffer that the owner ranks fill over
+  // NVLink while this kernel may already be running; every CTA first waits (bounded) until all n_wait
+  // flags have reached *epoch, and reads y through L2 only.
+  const unsigned* wait_flags;
+  const unsigned* epoch;
+  int n_wait;
+  long long wait_cycles;
+  int* status;
 };
 
 template <typename T> __device__ __forceinline__ void store_chunk(T* dst, const float (&f)[8]);
@@ -284,6 +297,10 @@ template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine
   const int t = blockIdx.x;
   pdl_wait();        // y comes from the down projection launched just before
   pdl_trigger();
+  const bool remote_y = p.wait_flags != nullptr;
+  if (remote_y && threadIdx.x >= 32 && threadIdx.x < 32 + p.n_wait) {
+    if (!ep_wait_flag(p.wait_flags + (threadIdx.x - 32), *p.epoch, p.wait_cycles)) atomicOr(p.status, kDevWaitExpired);
+  }
   // slot k of the token is read by thread k; thread 0 then orders the live ones by rank
   if (threadIdx.x < p.K) {
     const int k = threadIdx.x;
@@ -326,7 +343,10 @@ template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine
       for (int u = 0; u < 4; ++u) {
         if (j0 + u < n) {
           const int k = s_order[j0 + u];
-          if (p.ypart == nullptr) yc[u].template load<false>(y + (size_t)s_pos[k] * p.H + c * 8);
+          if (p.ypart == nullptr) {
+            if (remote_y) yc[u].load_cg(y + (size_t)s_pos[k] * p.H + c * 8);
+            else yc[u].template load<false>(y + (size_t)s_pos[k] * p.H + c * 8);
+          }
           w[u] = s_w[k];
         }
       }
@@ -368,39 +388,6 @@ template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine
       for (int i = 0; i < 8; ++i) acc[i] = rn<T>(__fadd_rn(rf[i], acc[i]));
     }
     store_chunk<T>(reinterpret_cast<T*>(p.out) + (size_t)t * p.H + c * 8, acc);
-  }
-}
-
-}  // namespace b200moe
-
-namespace b200moe {
-
-// Expert-parallel return leg: expert outputs from sorted-pair order back to pair order
-// (row t*K + k), zeros for pairs whose expert this rank does not serve.  Every row of `out` is
-// written, so the buffer needs no clearing and a sum over ranks reassembles all pairs exactly
-// (each row is non-zero on one rank only).
-struct ScatterParams {
-  const void* y;         // [pairs, H] sorted-pair order
-  const int* inv;        // [npairs]
-  const int64_t* ids64;  // [npairs]
-  void* out;             // [npairs, H]
-  int npairs, H, E;
-};
-
-template <typename T> __global__ void __launch_bounds__(kCombineThreads) scatter_pairs_kernel(ScatterParams p, SlotTable st) {
-  const int pr = blockIdx.x;
-  pdl_wait();
-  pdl_trigger();
-  const long long e = p.ids64[pr];
-  const int pos = (e >= 0 && e < p.E && st.slot[e] >= 0) ? p.inv[pr] : -1;
-  const T* y = reinterpret_cast<const T*>(p.y);
-  for (int c = threadIdx.x; c < p.H / 8; c += kCombineThreads) {
-    Chunk<T> v;
-    if (pos >= 0) v.template load<false>(y + (size_t)pos * p.H + c * 8);
-    else v.zero();
-    float f[8];
-    v.unpack(f);
-    store_chunk<T>(reinterpret_cast<T*>(p.out) + (size_t)pr * p.H + c * 8, f);
   }
 }
 

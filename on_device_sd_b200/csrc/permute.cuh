@@ -25,6 +25,16 @@ struct PermuteParams {
   int* act_list;     // [E] experts that have work (count > 0 and a usable slot), ascending
   int* n_act;        // [1]
   int* status;
+  // Expert-parallel source (ep_meta != null): the "pairs" are the rows of this rank's receive buffer,
+  // [ep_G][ep_cap] with K = 1; row j of source s holds expert ep_meta[s*cap+j].x when j < ep_count[s] and is
+  // padding otherwise.  The kernel first waits (bounded) until every source's dispatch flag has reached
+  // *ep_epoch.
+  const int2* ep_meta;
+  const int* ep_count;
+  const unsigned* ep_flags;
+  const unsigned* ep_epoch;
+  int ep_G, ep_cap;
+  long long ep_wait_cycles;
 };
 
 constexpr int kPermuteMaxThreads = 1024;
@@ -74,14 +84,31 @@ static __global__ void __launch_bounds__(kPermuteMaxThreads) permute_kernel(Perm
   for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) cnt[i] = 0;
   pdl_wait();        // ids come from the router launched just before
   pdl_trigger();
+  __shared__ int ep_cnt[8];
+  if (p.ep_meta != nullptr) {
+    if (threadIdx.x < p.ep_G) {
+      const bool ok = ep_wait_flag(p.ep_flags + threadIdx.x, *p.ep_epoch, p.ep_wait_cycles);
+      if (!ok) atomicOr(p.status, kDevWaitExpired);
+      ep_cnt[threadIdx.x] = ok ? max(0, min(__ldcg(p.ep_count + threadIdx.x), p.ep_cap)) : 0;
+    }
+  }
   __syncthreads();
+  // id of pair pr: -1 = padding (skipped silently), anything else outside [0,E) is reported
+  auto load_id = [&](int pr) -> long long {
+    if (p.ep_meta == nullptr) return p.ids64[pr];
+    const int s = pr / p.ep_cap, j = pr - s * p.ep_cap;
+    if (j >= ep_cnt[s]) return -1;
+    const int e = __ldcg(&p.ep_meta[pr]).x;
+    return (e < 0) ? -2 : e;
+  };
+  const bool pad_ok = p.ep_meta != nullptr;
 
   for (int b = begin; b < end; b += 32) {
     const int pr = b + lane;
     if (pr < end) {
-      const long long e = p.ids64[pr];
+      const long long e = load_id(pr);
       if (e >= 0 && e < E) atomicAdd(&cnt[warp * E + (int)e], 1);
-      else atomicOr(p.status, kDevBadExpertId);
+      else if (!(pad_ok && e == -1)) atomicOr(p.status, kDevBadExpertId);
     }
   }
   __syncthreads();
@@ -114,7 +141,7 @@ static __global__ void __launch_bounds__(kPermuteMaxThreads) permute_kernel(Perm
     const int pr = b + lane;
     long long e = -1;
     if (pr < end) {
-      e = p.ids64[pr];
+      e = load_id(pr);
       if (e < 0 || e >= E) e = -1;
     }
     const unsigned m = __match_any_sync(0xffffffffu, (int)e);

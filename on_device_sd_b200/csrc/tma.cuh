@@ -43,14 +43,27 @@ __device__ __forceinline__ bool mbar_try_wait_hint(uint64_t* bar, uint32_t parit
       : "memory");
   return ok != 0;
 }
-// Waits for the phase with the given parity, but never forever: after kSpinLimit failed polls
-// (each poll itself blocks for a hardware-defined slice) it gives up and returns false; the
-// caller records the failure in the status word and leaves.
-constexpr uint32_t kSpinLimit = 1u << 22;
+// Waits for the phase with the given parity, but never forever: the first probe costs one
+// instruction; after that the clock is read between probes (each probe suspends the warp for up
+// to 20 us) and the wait gives up after 2^31 cycles, about one second.  The caller records the
+// failure in the status word and leaves.
+constexpr long long kWaitCycleLimit = 1ll << 31;
 __device__ __forceinline__ bool mbar_wait_bounded(uint64_t* bar, uint32_t parity) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i)
+  if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+  const long long t0 = clock64();
+  for (;;) {
     if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
-  return false;
+    if (clock64() - t0 > kWaitCycleLimit) return false;
+  }
+}
+// A short, bounded wait (about 1 ms) used on an abort path to let copies that are already in
+// flight land before the warp gives its shared memory up.
+__device__ __forceinline__ bool mbar_wait_brief(uint64_t* bar, uint32_t parity) {
+  const long long t0 = clock64();
+  for (;;) {
+    if (mbar_try_wait_hint(bar, parity, 20000u)) return true;
+    if (clock64() - t0 > (1ll << 21)) return false;
+  }
 }
 
 __device__ __forceinline__ uint64_t l2_policy_evict_first() {

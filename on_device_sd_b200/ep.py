@@ -1,26 +1,28 @@
-"""Expert parallelism for the MoE block: experts sharded across ranks, tokens exchanged over NCCL.
+"""Expert parallelism for the MoE block: experts sharded across ranks, tokens and results exchanged by
+the library's own kernels through peer memory over NVLink.
 
 Not in the reference (single GPU; "expert distribution across GPUs" is future work there,
-demo/others.md:58-62).  One process per GPU, torch.distributed for the plumbing:
+demo/others.md:58-62).  One process per GPU; torch.distributed is the plumbing only - it carries the
+64-byte buffer handles at set-up and the barriers around it, never a token:
 
     rank r owns experts [r*E/G, (r+1)*E/G); the router weight is replicated.
-    1. route        each rank routes its own T/G tokens                      (K1, local)
-    2. dispatch     all-gather of x and of the ids: with top-8 over 8 ranks a token is needed by
-                    ~5 ranks out of 8, so gathering every token everywhere IS the dispatch; both
-                    collectives have fixed sizes, so no count exchange and no host sync
-    3. experts      FFN of the local experts over every rank's tokens; outputs written in pair order
-                    (row t*K+k), zeros for pairs served elsewhere                (K2, K3, scatter)
-    4. return       sum reduce-scatter of the pair buffers: every row is non-zero on exactly one
-                    rank, so the sum is exact, and each rank receives the rows of its own tokens
-    5. combine      weighted accumulation in the model dtype, same order as on one GPU (K4, local)
+    1. route      each rank routes its own T/G tokens                                     (K1, local)
+    2. dispatch   every (token, expert) pair's row is stored straight into the owner rank's receive
+                  region for this source, then a count and an epoch flag                   (peer stores)
+    3. experts    the owner waits for all sources' flags, groups the received rows by expert and runs
+                  its local experts over its LOCAL receive buffer                          (K2, K3)
+    4. return     every output row is stored straight into its source rank's return rows, then a flag
+    5. combine    the source waits for all owners' flags and accumulates in the model dtype, in the
+                  same order as on one GPU                                                 (K4, local)
 
-The result is bit-identical to the single-GPU result for any number of ranks, because every
-expert output row is computed by the same kernel on the same inputs and the combine sees the same
-rows in the same order.
+The result is bit-identical to the single-GPU result: every expert output row is computed by the same
+kernel on the same inputs and the combine sees the same rows in the same order.  Every rank must make
+the same sequence of layer calls; a rank that never arrives makes the others' bounded waits run out
+(status B200MOE_DEV_WAIT_EXPIRED), it cannot hang them.
 """
 from __future__ import annotations
 
-from typing import Any, Dict, Optional, Sequence
+from typing import Any, Dict, List, Optional, Sequence
 
 import torch
 import torch.distributed as dist
@@ -46,21 +48,34 @@ def split_tokens(T: int, world: int, rank: int) -> range:
     return range(rank * per, (rank + 1) * per)
 
 
+def exchange_handles(handle: bytes, group: Optional[dist.ProcessGroup] = None) -> List[bytes]:
+    """All ranks' buffer handles, rank-major.  The one piece of host plumbing of the data plane."""
+    world = dist.get_world_size(group)
+    out: List[Any] = [None] * world
+    dist.all_gather_object(out, bytes(handle), group=group)
+    return [bytes(h) for h in out]
+
+
 class ExpertParallelMoE:
     """One rank of an expert-parallel MoE block.
 
-    `ctx` supplies the three local steps: route(layer, x) -> (ids, scores);
-    ep_local_experts(layer, x_all, ids_all) -> y_pairs [T_all*K, H]; ep_combine(y_pairs, ids,
-    scores, order=, residual=) -> out.  On a GPU that is a MoEContext; the CPU tests of the
-    collective plumbing pass a stand-in with the same three methods.
+    `ctx` supplies ep_create(world, rank, max_local_tokens) -> handle, ep_attach(handles),
+    ep_forward(layer, x_local, order=, residual=) -> out, ep_detach() and set_expert.  On a GPU that is a
+    MoEContext; the CPU test of the exchange protocol passes a stand-in with the same methods.
     """
 
-    def __init__(self, ctx: Any, num_experts: int, top_k: int, hidden_size: int, group: Optional[dist.ProcessGroup] = None):
+    def __init__(self, ctx: Any, num_experts: int, top_k: int, hidden_size: int, max_local_tokens: int,
+                 group: Optional[dist.ProcessGroup] = None):
         self.ctx, self.E, self.K, self.H = ctx, num_experts, top_k, hidden_size
         self.group = group
         self.world = dist.get_world_size(group)
         self.rank = dist.get_rank(group)
         self.local_experts = expert_range(num_experts, self.world, self.rank)
+        self.max_local_tokens = max_local_tokens
+        handle = ctx.ep_create(self.world, self.rank, max_local_tokens)
+        if self.world > 1:
+            ctx.ep_attach(exchange_handles(handle, group))
+            dist.barrier(group)          # every rank has mapped every buffer before anyone stores into one
 
     def register_local_experts(self, layer: int, experts: Dict[int, Dict[str, torch.Tensor]]) -> None:
         """Registers the experts this rank owns (others in `experts` are ignored)."""
@@ -71,16 +86,10 @@ class ExpertParallelMoE:
     def forward(self, layer: int, x_local: torch.Tensor, *, residual: Optional[torch.Tensor] = None,
                 order: Optional[Sequence[int]] = None) -> torch.Tensor:
         """x_local [T/G, H] (this rank's tokens) -> [T/G, H]."""
-        Tl = x_local.shape[0]
-        ids, scores = self.ctx.route(layer, x_local)
-        if self.world == 1:
-            y_pairs = self.ctx.ep_local_experts(layer, x_local, ids)
-            return self.ctx.ep_combine(y_pairs, ids, scores, order=order, residual=residual)
-        x_all = torch.empty(Tl * self.world, self.H, dtype=x_local.dtype, device=x_local.device)
-        ids_all = torch.empty(Tl * self.world, self.K, dtype=torch.int64, device=x_local.device)
-        dist.all_gather_into_tensor(x_all, x_local.contiguous(), group=self.group)
-        dist.all_gather_into_tensor(ids_all, ids, group=self.group)
-        y_pairs = self.ctx.ep_local_experts(layer, x_all, ids_all)          # [T*K, H], zeros where not served here
-        y_own = torch.empty(Tl * self.K, self.H, dtype=x_local.dtype, device=x_local.device)
-        dist.reduce_scatter_tensor(y_own, y_pairs, op=dist.ReduceOp.SUM, group=self.group)
-        return self.ctx.ep_combine(y_own, ids, scores, order=order, residual=residual)
+        return self.ctx.ep_forward(layer, x_local, order=order, residual=residual)
+
+    def close(self) -> None:
+        """Unmaps the peers' buffers; call on every rank before the contexts go away."""
+        if self.world > 1:
+            dist.barrier(self.group)     # nobody is still storing into a buffer that is about to be unmapped
+        self.ctx.ep_detach()

@@ -29,3 +29,14 @@ def expert_forward_noalloc(x: torch.Tensor, gate_weight: torch.Tensor, up_weight
         check(None, _lib.load().b200moe_expert_ffn_noalloc(_ptr(x), n, H, I, dtype_tag(x.dtype), _ptr(gate_weight), _ptr(up_weight),
                                                            _ptr(down_weight), _ptr(out), _stream(x.device)))
     return out
+
+
+def noalloc_status(device: torch.device) -> int:
+    """Waits for the current stream of `device` and returns the status word of the latest
+    expert_forward_noalloc call there (0 = clean); raises B200MoEError when a kernel's bounded wait
+    gave up.  Allocates nothing either."""
+    import ctypes
+    v = ctypes.c_int(0)
+    with torch.cuda.device(device):
+        check(None, _lib.load().b200moe_expert_ffn_noalloc_status(ctypes.byref(v), _stream(torch.device(device))))
+    return v.value

@@ -15,6 +15,7 @@ methods to an instance of this class unchanged.
 """
 from __future__ import annotations
 
+from collections import OrderedDict
 from typing import Any, Dict, List, Optional, Sequence
 
 import torch
@@ -99,7 +100,9 @@ class B200MoERunner:
         graph_blocks=True makes `moe_block` capture its kernels into a CUDA graph the first time it sees
         an input buffer (keyed by layer, address, shape and residual address) and replay it afterwards:
         one launch per block instead of five.  The result then lives in a buffer owned by the runner that
-        the next call with the same key overwrites, and the experts must not be re-registered in between."""
+        the next call with the same key overwrites.  A graph bakes the registered pointers in, so every
+        graph is dropped as soon as a gate or an expert is registered, moved or cleared (the context
+        counts such changes), and at most `max_graphs` graphs are kept, least recently used first out."""
         self.config = config
         self.dtype = config.get_dtype()
         self.expert_id_cls = expert_id_cls
@@ -113,7 +116,9 @@ class B200MoERunner:
         self._gate_w: Dict[int, torch.Tensor] = {}
         self._last_layer = 0
         self.graph_blocks = graph_blocks
-        self._graphs: Dict[tuple, tuple] = {}
+        self.max_graphs = 64
+        self._graphs: "OrderedDict[tuple, tuple]" = OrderedDict()
+        self._graphs_generation = -1
 
     def get_config(self):
         return self.config
@@ -201,7 +206,12 @@ class B200MoERunner:
         res2d = None if residual is None else residual.reshape(-1, h)
         if self.graph_blocks and not return_routing and flat.is_contiguous() and (res2d is None or res2d.is_contiguous()):
             key = (layer_idx, flat.data_ptr(), tuple(flat.shape), None if res2d is None else res2d.data_ptr())
+            if self._graphs_generation != self.ctx.generation:     # a registered pointer changed: every captured graph is stale
+                self._graphs.clear()
+                self._graphs_generation = self.ctx.generation
             hit = self._graphs.get(key)
+            if hit is not None:
+                self._graphs.move_to_end(key)
             if hit is None:
                 for _ in range(2):                       # warm-up outside the capture (lazy kernel attributes, tensor maps)
                     self.ctx.forward_fused(layer_idx, flat, residual=res2d, ffn_kind=self.ffn_kind)
@@ -211,6 +221,8 @@ class B200MoERunner:
                     out = self.ctx.forward_fused(layer_idx, flat, residual=res2d, ffn_kind=self.ffn_kind)
                 hit = (g, out)
                 self._graphs[key] = hit
+                while len(self._graphs) > self.max_graphs:
+                    self._graphs.popitem(last=False)
             hit[0].replay()
             return hit[1].view(hidden_states.shape)
         r = self.ctx.forward_fused(layer_idx, flat, residual=res2d, return_routing=return_routing, ffn_kind=self.ffn_kind)

@@ -2,7 +2,7 @@
 
 This is the shape of the engine's verify loop (demo/src/execution/cb_executor.py:406-450 of the
 reference: per layer forward_attention -> route_experts -> forward_moe) with everything but the MoE
-block removed, used to measure the block at model depth (BASELINE's 48-layer configuration).  The
+block removed, used to measure the block at model depth (48 layers of the Qwen3-30B-A3B shape).  The
 residual add of forward_moe (demo/src/model/qwen3_runner.py:226) is kept and fused into the combine
 kernel; norms are skipped.  Because there are no norms, the residual stream is re-anchored at the
 input tokens x in every block (with random-init weights h <- h + MoE(h) squares its magnitude every

@@ -187,3 +187,15 @@ def test_moe_block_graph_replay_equals_eager_launches():
         assert torch.equal(got, want), trial
         x.copy_(torch.randn(T, H, generator=torch.Generator().manual_seed(trial)).bfloat16())   # same buffer, new tokens
     assert len(graphed._graphs) == 1 and eager.ctx.status() == 0 and graphed.ctx.status() == 0
+    # re-registering an expert at a new address drops the captured graphs: the replay must see the new weights
+    moved = {k: (v.cuda() * 2).contiguous() for k, v in L.experts[0].items()}
+    for r in (eager, graphed):
+        r.register_experts(0, {0: moved})
+    assert torch.equal(graphed.moe_block(0, x, residual=res), eager.moe_block(0, x, residual=res))
+    assert len(graphed._graphs) == 1
+    # the cache is bounded: least recently used graphs go first
+    graphed.max_graphs = 2
+    bufs = [x.clone() for _ in range(4)]
+    for b in bufs:
+        graphed.moe_block(0, b)
+    assert len(graphed._graphs) == 2
