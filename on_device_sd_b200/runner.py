@@ -85,6 +85,42 @@ def plan_placement(expert_placement: Any, num_experts: int):
     return avail, slot, order
 
 
+class LazyRoutingResult(RoutingResult):
+    """RoutingResult whose `activated_expert_ids` set is built when it is first read.
+
+    The reference builds the set inside route_experts with .unique().tolist() - one device
+    synchronisation per layer whether or not anybody looks at the set (qwen3_runner.py:110-112).
+    Here the router kernel writes one bit per selected expert into pinned host memory; reading the
+    attribute waits for that copy (an event, not the whole stream) and inserts ExpertID(layer, e) in
+    ascending e, the insertion order of the reference, so the set iterates in the same order."""
+
+    def __init__(self, layer_idx: int, topk_indices: torch.Tensor, topk_scores: torch.Tensor, bitmap: torch.Tensor,
+                 ready: "torch.cuda.Event", expert_id_cls: type):
+        self.layer_idx, self.topk_indices, self.topk_scores = layer_idx, topk_indices, topk_scores
+        self._bitmap, self._ready, self._cls, self._set = bitmap, ready, expert_id_cls, None
+
+    @property
+    def activated_expert_ids(self):
+        if self._set is None:
+            self._ready.synchronize()
+            s = set()
+            for w in range(4):
+                bits = int(self._bitmap[w]) & 0xFFFFFFFFFFFFFFFF
+                while bits:
+                    low = bits & -bits
+                    s.add(self._cls(self.layer_idx, w * 64 + low.bit_length() - 1))
+                    bits ^= low
+            self._set = s
+        return self._set
+
+    @activated_expert_ids.setter
+    def activated_expert_ids(self, value):
+        self._set = value
+
+    def __repr__(self):
+        return f"LazyRoutingResult(layer_idx={self.layer_idx}, tokens={tuple(self.topk_indices.shape)})"
+
+
 class B200MoERunner:
     def __init__(self, config: Any, *, device: Optional[torch.device] = None, max_tokens: int = 512,
                  weight_mode: int = W_DENSE, expert_id_cls: type = ExpertID, exact_logits: bool = False,
@@ -112,7 +148,8 @@ class B200MoERunner:
                               config.moe_intermediate_size, self.dtype, num_layers=config.num_hidden_layers,
                               max_tokens=max_tokens, weight_mode=weight_mode, device=device)
         self.device = self.ctx.device
-        self._bitmap = torch.zeros(4, dtype=torch.int64).pin_memory()
+        # per layer: expert -> (params dict object, address of its gate_proj) as last registered through a placement
+        self._placed: Dict[int, Dict[int, tuple]] = {}
         self._gate_w: Dict[int, torch.Tensor] = {}
         self._last_layer = 0
         self.graph_blocks = graph_blocks
@@ -134,6 +171,7 @@ class B200MoERunner:
         self._gate_w[layer_idx] = self.ctx._gate[layer_idx][0]
 
     def register_experts(self, layer_idx: int, experts: Dict[int, Dict[str, torch.Tensor]]) -> None:
+        self._placed.pop(layer_idx, None)
         for e, params in experts.items():
             self.ctx.set_expert(layer_idx, e, params)
 
@@ -143,25 +181,19 @@ class B200MoERunner:
         flat = hidden_states.reshape(-1, h)
         if not flat.is_contiguous():
             raise ValueError("hidden_states must be contiguous")
+        bitmap = torch.empty(4, dtype=torch.int64, pin_memory=True)      # host-pinned blocks are recycled by torch's allocator
         if self.exact_logits:
             logits = torch.nn.functional.linear(flat, self._gate_w[layer_idx])
             bias = self.ctx._gate[layer_idx][1]
             if bias is not None:
                 logits = logits + bias
-            ids, scores = self.ctx.route(layer_idx, flat, bitmap=self._bitmap, logits=logits)
+            ids, scores = self.ctx.route(layer_idx, flat, bitmap=bitmap, logits=logits)
         else:
-            ids, scores = self.ctx.route(layer_idx, flat, bitmap=self._bitmap)
-        # the reference builds the activated set with .unique().tolist() - one device sync per layer
-        torch.cuda.current_stream(self.device).synchronize()
-        activated = set()
-        for w in range(4):
-            bits = int(self._bitmap[w].item()) & 0xFFFFFFFFFFFFFFFF
-            while bits:
-                low = bits & -bits
-                activated.add(self.expert_id_cls(layer_idx, w * 64 + low.bit_length() - 1))
-                bits ^= low
+            ids, scores = self.ctx.route(layer_idx, flat, bitmap=bitmap)
+        ready = torch.cuda.Event()
+        ready.record(torch.cuda.current_stream(self.device))
         self._last_layer = layer_idx
-        return RoutingResult(layer_idx=layer_idx, topk_indices=ids, topk_scores=scores, activated_expert_ids=activated)
+        return LazyRoutingResult(layer_idx, ids, scores, bitmap, ready, self.expert_id_cls)
 
     def forward_moe(self, layer_idx: int, attn_output: Any, expert_placement: Any) -> torch.Tensor:
         """residual + MoE(post_attn_normed); the add is fused into the combine kernel."""
@@ -180,8 +212,16 @@ class B200MoERunner:
         flat = hidden_states.reshape(-1, h)
 
         avail, slot, order = plan_placement(expert_placement, E)
-        for e in sorted({s for s in slot if s >= 0}):
-            self.ctx.set_expert(layer, e, self._prepare_params(avail[e]))
+        placed = self._placed.setdefault(layer, {})
+        for e in {s for s in slot if s >= 0}:
+            params = avail[e]
+            hit = placed.get(e)
+            # the engine hands over the same per-expert dict object call after call while the expert stays resident:
+            # one identity check and one address check instead of three shape / device / pointer comparisons
+            if hit is not None and hit[0] is params and hit[1] == params["gate_proj"].data_ptr():
+                continue
+            self.ctx.set_expert(layer, e, self._prepare_params(params))
+            placed[e] = (params, params["gate_proj"].data_ptr())
         res2d = None if residual is None else residual.reshape(-1, h)
         out = self.ctx.forward(layer, flat, routing.topk_indices, routing.topk_scores, expert_slot=slot, order=order,
                                residual=res2d, ffn_kind=self.ffn_kind)
