@@ -133,6 +133,12 @@ int b200moe_last_logits(b200moe_ctx* ctx, int T, float* logits_out, void* stream
 int b200moe_last_tables(b200moe_ctx* ctx, int T, int32_t* offsets_out, int32_t* sorted_pair_out, int32_t* inv_out,
                         int32_t* act_list_out, int32_t* n_act_out, void* stream);
 
+/* K2 alone: groups the (token, slot) pairs of ids [T,K] by expert and copies the result to tables_out
+ * (int32, device or pinned host): offsets [E+1] followed by sorted_pair [T*K] as described above; ids
+ * outside [0,E) are dropped.  It is the device form of the K x E loop of torch.where calls with which
+ * the reference builds LayerExpertActivations (demo/src/execution/model_runner_utils.py:13-41). */
+int b200moe_group_pairs(b200moe_ctx* ctx, const int64_t* ids, int T, int32_t* tables_out, void* stream);
+
 /* Expert execution for a given routing: Qwen3ModelRunner._execute_moe_with_placement
  * (demo/src/model/qwen3_runner.py:269-385) plus, with `residual`, forward_moe's add (:226).
  *   x [T,H]; ids int64 [T,K]; scores [T,K] of scores_dtype (activation dtype or B200MOE_F32);
@@ -154,6 +160,22 @@ int b200moe_forward(b200moe_ctx* ctx, int layer, const void* x, int T, const int
  * (demo/src/layers/moe_layer.py:93-170) in one enqueue.  ids_out / scores_out may be NULL. */
 int b200moe_forward_fused(b200moe_ctx* ctx, int layer, const void* x, int T, const void* residual, void* out,
                           int64_t* ids_out, void* scores_out, int ffn_kind, void* stream);
+
+/* The decoder layer's post-attention RMSNorm, the router, the experts, the combine and the residual add
+ * in one enqueue: what the reference does with `post_attention_layernorm` at the end of forward_attention
+ * (demo/src/model/qwen3_runner.py:204, demo/src/layers/layernorm.py:21-36), route_experts (:86-119) and
+ * forward_moe (:212-226).  The norm is fused into the router kernel's load of the tokens; no separate
+ * norm launch and no extra pass over [T,H].
+ *   s = hidden (+ residual);  new_residual = T(s);  normed = T( T(s * rsqrt(mean(s^2) + eps)) * norm_weight )
+ *   out = new_residual + MoE(normed)
+ *   hidden, residual (may be NULL), out [T,H]; norm_weight [H]; all in the activation dtype.
+ *   residual_out / normed_out (device, [T,H]) receive new_residual / normed when not NULL;
+ *   ids_out / scores_out as in b200moe_forward_fused.
+ * normed equals b200moe_rmsnorm's output bit for bit (same code), the rest equals b200moe_forward_fused
+ * on it. */
+int b200moe_forward_fused_norm(b200moe_ctx* ctx, int layer, const void* hidden, const void* residual, const void* norm_weight, float eps,
+                               int T, void* out, void* residual_out, void* normed_out, int64_t* ids_out, void* scores_out, int ffn_kind,
+                               void* stream);
 
 /* Expert parallelism.  No counterpart in the reference, which runs on one GPU ("expert distribution
  * across GPUs" is future work there, demo/others.md:58-62); the single-GPU result is the oracle.

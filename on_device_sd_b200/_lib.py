@@ -47,6 +47,8 @@ PROTOTYPES = {
     "b200moe_forward": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_int, POINTER(c_int32),
                                 POINTER(c_int32), c_void_p, c_void_p, c_int, c_void_p]),
     "b200moe_forward_fused": (c_int, [c_void_p, c_int, c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_int, c_void_p]),
+    "b200moe_forward_fused_norm": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_float, c_int, c_void_p, c_void_p, c_void_p, c_void_p,
+                                           c_void_p, c_int, c_void_p]),
     "b200moe_ep_create": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p]),
     "b200moe_ep_attach_ipc": (c_int, [c_void_p, c_void_p]),
     "b200moe_ep_attach_local": (c_int, [c_void_p, POINTER(c_void_p)]),
@@ -62,6 +64,7 @@ PROTOTYPES = {
     "b200moe_expert_ffn_noalloc": (c_int, [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
     "b200moe_expert_ffn_noalloc_status": (c_int, [POINTER(c_int), c_void_p]),
     "b200moe_last_tables": (c_int, [c_void_p, c_int, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p, c_void_p]),
+    "b200moe_group_pairs": (c_int, [c_void_p, c_void_p, c_int, c_void_p, c_void_p]),
     "b200moe_pack_int4": (c_int, [c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_unpack_int4": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_profile": (c_int, [c_void_p, c_int]),

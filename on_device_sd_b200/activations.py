@@ -2,9 +2,10 @@
 
 The reference builds the same object with a K x E loop of ``torch.where`` calls, each a device
 synchronisation (demo/src/execution/model_runner_utils.py:13-41; up to 1024 per layer for the
-128-expert model).  Here the ids cross to the host once, the (k, expert, token) grouping is a stable
-sort on the host, and the token lists and scores of all activations are slices of two tensors sent
-back in one copy and one gather.  Order and contents equal the reference's: activations sorted by
+128-expert model).  With a context (`ctx=`) the grouping kernel of the MoE block (K2) sorts the
+(token, slot) pairs by expert on the device and its two tables cross to the host in one copy; without
+one the ids themselves cross once and are grouped on the host.  Either way the token lists and scores
+of all activations are slices of two tensors sent back in one copy and one gather.  Order and contents equal the reference's: activations sorted by
 top-k rank, then expert index; ``token_indices`` ascending int64 on the ids' device; ``scores`` =
 ``topk_scores[token_indices, k]``; ``routing_scores`` is the RoutingResult's ``topk_scores``.
 """
@@ -19,7 +20,7 @@ from .types import ExpertActivation, ExpertID, LayerExpertActivations
 
 
 def build_layer_activations(routing_result: Any, num_experts: int, *,
-                            expert_id_cls: Optional[Callable[[int, int], Any]] = None) -> LayerExpertActivations:
+                            expert_id_cls: Optional[Callable[[int, int], Any]] = None, ctx: Any = None) -> LayerExpertActivations:
     ids = routing_result.topk_indices
     scores = routing_result.topk_scores
     layer = routing_result.layer_idx
@@ -28,10 +29,15 @@ def build_layer_activations(routing_result: Any, num_experts: int, *,
     if T == 0 or K == 0:
         return LayerExpertActivations(layer_idx=layer, activations=[], routing_scores=scores)
 
-    ids_h = ids.detach().to("cpu", non_blocking=False).numpy()                     # the one device->host copy
-    # ids outside [0, num_experts) never match the reference's `== expert_idx` test: drop them.
-    t_idx, k_idx = np.nonzero((ids_h >= 0) & (ids_h < num_experts))
-    e_idx = ids_h[t_idx, k_idx]
+    if ctx is not None and ids.is_cuda and ids.dtype == torch.int64 and ids.is_contiguous() and (ctx.E, ctx.K) == (num_experts, K) and T <= ctx.max_tokens:
+        offsets, pairs = ctx.group_pairs(ids)                                        # K2's tables: the one device->host copy
+        e_idx = np.repeat(np.arange(num_experts, dtype=np.int64), np.diff(offsets))  # pairs are grouped by expert, row-major inside
+        t_idx, k_idx = np.divmod(pairs.astype(np.int64), K)
+    else:
+        ids_h = ids.detach().to("cpu", non_blocking=False).numpy()                   # the one device->host copy
+        # ids outside [0, num_experts) never match the reference's `== expert_idx` test: drop them.
+        t_idx, k_idx = np.nonzero((ids_h >= 0) & (ids_h < num_experts))
+        e_idx = ids_h[t_idx, k_idx]
     key = k_idx.astype(np.int64) * num_experts + e_idx
     order = np.argsort(key, kind="stable")                                           # tokens stay ascending inside a key
     key, t_sorted, k_sorted = key[order], t_idx[order], k_idx[order]

@@ -171,6 +171,17 @@ class MoEContext:
         self._check(self._lib.b200moe_last_tables(self._h, T, _ptr(offsets), _ptr(sp), _ptr(inv), _ptr(act), _ptr(n_act), _stream(self.device)))
         return offsets, sp, inv, act[: int(n_act.item())]
 
+    def group_pairs(self, ids: torch.Tensor):
+        """K2 on its own: (offsets [E+1], sorted_pair [valid pairs]) as int32 numpy arrays, through ONE device->host copy."""
+        _need_cuda(ids, "ids", self.device, torch.int64)
+        T = ids.shape[0]
+        tables = torch.empty(self.E + 1 + T * self.K, dtype=torch.int32, pin_memory=True)
+        self._check(self._lib.b200moe_group_pairs(self._h, _ptr(ids), T, _ptr(tables), _stream(self.device)))
+        torch.cuda.current_stream(self.device).synchronize()
+        t = tables.numpy()
+        offsets = t[: self.E + 1]
+        return offsets, t[self.E + 1: self.E + 1 + int(offsets[-1])]
+
     def forward(self, layer: int, x2d: torch.Tensor, ids: torch.Tensor, scores: torch.Tensor, *,
                 expert_slot: Optional[Sequence[int]] = None, order: Optional[Sequence[int]] = None,
                 residual: Optional[torch.Tensor] = None, ffn_kind: int = FFN_AUTO) -> torch.Tensor:
@@ -210,6 +221,27 @@ class MoEContext:
         self._check(self._lib.b200moe_forward_fused(self._h, layer, _ptr(x2d), T, _ptr(residual), _ptr(out), _ptr(ids), _ptr(scores),
                                                     ffn_kind, _stream(self.device)))
         return (out, ids, scores) if return_routing else out
+
+    def forward_fused_norm(self, layer: int, hidden: torch.Tensor, norm_weight: torch.Tensor, eps: float, *,
+                           residual: Optional[torch.Tensor] = None, return_parts: bool = False, ffn_kind: int = FFN_AUTO):
+        """RMSNorm (+ residual add) -> router -> experts -> combine -> + new residual, one enqueue.
+        Returns out, or (out, new_residual, normed, ids, scores) with return_parts."""
+        _need_cuda(hidden, "hidden", self.device, self.dtype)
+        _need_cuda(norm_weight, "norm_weight", self.device, self.dtype)
+        if residual is not None:
+            _need_cuda(residual, "residual", self.device, self.dtype)
+        T = hidden.shape[0]
+        if hidden.shape != (T, self.H) or norm_weight.shape != (self.H,):
+            raise ValueError(f"hidden must be [T,{self.H}] and norm_weight [{self.H}]")
+        out = torch.empty_like(hidden)
+        res_out = normed = ids = scores = None
+        if return_parts:
+            res_out, normed = torch.empty_like(hidden), torch.empty_like(hidden)
+            ids = torch.empty(T, self.K, dtype=torch.int64, device=self.device)
+            scores = torch.empty(T, self.K, dtype=self.dtype, device=self.device)
+        self._check(self._lib.b200moe_forward_fused_norm(self._h, layer, _ptr(hidden), _ptr(residual), _ptr(norm_weight), float(eps), T, _ptr(out),
+                                                         _ptr(res_out), _ptr(normed), _ptr(ids), _ptr(scores), ffn_kind, _stream(self.device)))
+        return (out, res_out, normed, ids, scores) if return_parts else out
 
     # -- expert parallelism (peer-store dispatch / return; include/b200moe.h) -----------------------
     def ep_create(self, world: int, rank: int, max_local_tokens: int) -> bytes:

@@ -66,6 +66,8 @@ struct b200moe_ctx {
   int* n_act = nullptr;
   void* h = nullptr;
   void* y = nullptr;
+  void* xnorm = nullptr;            // fused-norm entry: normalised token rows [Tm, H]
+  void* xres = nullptr;             // fused-norm entry: x + residual rounded to the model dtype [Tm, H]
   void* xperm = nullptr;            // int4 tcgen05 path: k-permuted token rows in sorted-pair order [Tm*K, H]
   float* ypart = nullptr;           // fp32 K-slices of the down projection (tensor-core path)
   int ypart_slices = 0;             // slices ypart has room for
@@ -219,7 +221,7 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
   char* sb = nullptr;
   const size_t pairs = Tm * K;
   if ((rc = dev_alloc(ctx, &ctx->d_experts, L * E + 1)) || (rc = dev_alloc(ctx, &ctx->logits, Tm * E)) ||
-      (rc = dev_alloc(ctx, &ctx->tile_counter, Tm)) || (rc = dev_alloc(ctx, &ctx->ids64, pairs)) ||
+      (rc = dev_alloc(ctx, &ctx->tile_counter, Tm + 1)) || (rc = dev_alloc(ctx, &ctx->ids64, pairs)) ||
       (rc = dev_alloc(ctx, &sb, pairs * 4)) || (rc = dev_alloc(ctx, &ctx->offsets, (size_t)E + 1)) ||
       (rc = dev_alloc(ctx, &ctx->sorted_pair, pairs)) || (rc = dev_alloc(ctx, &ctx->inv, pairs)) ||
       (rc = dev_alloc(ctx, &ctx->act_list, (size_t)E)) || (rc = dev_alloc(ctx, &ctx->n_act, 4)) ||
@@ -234,6 +236,17 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
   ctx->h = hb;
   ctx->y = yb;
   ctx->scores = sb;
+  {
+    char* xn = nullptr;
+    char* xr = nullptr;
+    if ((rc = dev_alloc(ctx, &xn, Tm * (size_t)H * eb)) || (rc = dev_alloc(ctx, &xr, Tm * (size_t)H * eb))) {
+      std::string msg = ctx->err;
+      b200moe_destroy(ctx);
+      return fail(nullptr, rc, "%s", msg.c_str());
+    }
+    ctx->xnorm = xn;
+    ctx->xres = xr;
+  }
 #ifdef B200MOE_WITH_UMMA
   if (cfg->act_dtype == B200MOE_BF16 || (cfg->act_dtype == B200MOE_F16 && cfg->weight_mode == B200MOE_W_DENSE)) {   // dense bf16 / fp16 (tcgen05 path) and int4 (TMA boxes of packed nibbles)
     ctx->h_tmaps.assign((L * E + 1) * 3, CUtensorMap{});
@@ -269,7 +282,7 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
       ctx->encode_fn = nullptr;   // the tensor-core path then reports itself unsupported
   }
 #endif
-  cudaMemset(ctx->tile_counter, 0, Tm * sizeof(unsigned));
+  cudaMemset(ctx->tile_counter, 0, (Tm + 1) * sizeof(unsigned));
   cudaMemset(ctx->status, 0, sizeof(int));
   cudaMemset(ctx->d_experts, 0, (L * E + 1) * sizeof(ExpertPtrs));
   {
@@ -432,8 +445,34 @@ extern "C" int b200moe_clear_expert(b200moe_ctx* ctx, int layer, int expert) {
 // ------------------------------------------------------------------------------------------
 // router
 // ------------------------------------------------------------------------------------------
+// The opt-in dynamic shared-memory size is a property of a kernel ON ONE DEVICE: remember per template
+// instance which devices have been configured (one bit each), not just that some device was.
+struct ConfiguredDevices {
+  std::atomic<unsigned long long> mask{0};
+  bool needs(int device) const { return device < 0 || device >= 64 || !((mask.load(std::memory_order_acquire) >> device) & 1ull); }
+  void done(int device) { if (device >= 0 && device < 64) mask.fetch_or(1ull << device, std::memory_order_release); }
+};
+
+static void identity_slots(SlotTable& tab) {
+  for (int e = 0; e < kMaxExperts; ++e) { tab.slot[e] = -1; tab.rank[e] = (uint8_t)(e & 255); }
+}
+
+// Largest batch (in pairs) whose grouping the router's last CTA takes over: its 256 threads group that
+// many pairs about as fast as the separate kernel's CTA does, and one launch plus one dependency edge go.
+constexpr int kFusePermuteMaxPairs = 512;
+
+// `fuse` (with `tab`): the grouping tables of the batch are built by the router grid itself.
+struct RouterNorm {          // RMSNorm fused into the router's load of the tokens (null weight = off)
+  const void* residual = nullptr;
+  const void* weight = nullptr;
+  float eps = 0.0f;
+  void* normed_out = nullptr;
+  void* res_out = nullptr;
+};
+
 static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void* logits, int T, int64_t* ids_out,
-                         void* scores_out, unsigned long long* bitmap_dev, cudaStream_t st) {
+                         void* scores_out, unsigned long long* bitmap_dev, cudaStream_t st, const PermuteParams* fuse = nullptr,
+                         const SlotTable* tab = nullptr, const RouterNorm* norm = nullptr) {
   const b200moe_config& c = ctx->cfg;
   RouterParams p{};
   p.x = x;
@@ -448,6 +487,16 @@ static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void*
   p.scores = scores_out;
   p.bitmap = bitmap_dev;
   p.T = T; p.H = c.hidden_size; p.E = c.num_experts; p.K = c.top_k;
+  p.all_done = ctx->tile_counter + c.max_tokens;
+  const bool with_norm = norm != nullptr && norm->weight != nullptr;
+  if (with_norm) {
+    p.norm_res = norm->residual; p.norm_w = norm->weight; p.norm_eps = norm->eps; p.normed_out = norm->normed_out; p.res_out = norm->res_out;
+    if (c.hidden_size % 8 || c.hidden_size > kNormThreads * kNormMaxChunks * 8)
+      return fail(ctx, B200MOE_E_UNSUPPORTED, "fused norm: hidden size %d (multiples of 8 up to %d)", c.hidden_size, kNormThreads * kNormMaxChunks * 8);
+  }
+  SlotTable none;
+  if (fuse && tab) { p.fuse_permute = 1; p.perm = *fuse; }
+  else { identity_slots(none); tab = &none; }
   return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
     using Tt = decltype(tag);
     ProfScope prof(ctx, B200MOE_KERNEL_ROUTER, st);
@@ -455,13 +504,43 @@ static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void*
       launch_chain(router_from_logits_kernel<Tt>, dim3((T + 7) / 8), dim3(kRouterThreads), 0, st, p);
       return post_launch(ctx, "router_from_logits_kernel");
     }
-    const unsigned ey = (c.num_experts + 7) / 8;
-    if ((long long)T * ey <= 2LL * ctx->sm_count) {   // small batch: one token per tile, deep unroll
-      launch_chain(router_kernel<Tt, 1, 8>, dim3(T, ey), dim3(kRouterThreads), 0, st, p);
-    } else {
-      launch_chain(router_kernel<Tt, 4, 2>, dim3((T + 3) / 4, ey), dim3(kRouterThreads), 0, st, p);
+    if (T <= 16) {   // small batch: one token per tile, every load of a row in flight at once
+      const unsigned ey = (c.num_experts + 7) / 8;
+      if (with_norm) {
+        const size_t row = (size_t)c.hidden_size * sizeof(Tt);
+        auto kn = router_kernel<Tt, 1, 8, true>;
+        static ConfiguredDevices configured_n;
+        if (configured_n.needs(c.device)) {
+          CUDA_TRY(ctx, cudaFuncSetAttribute(kn, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
+          configured_n.done(c.device);
+        }
+        launch_chain(kn, dim3(T, ey), dim3(kRouterThreads), row, st, p, *tab);
+      } else {
+        launch_chain(router_kernel<Tt, 1, 8>, dim3(T, ey), dim3(kRouterThreads), 0, st, p, *tab);
+      }
+      return post_launch(ctx, "router_kernel");
     }
-    return post_launch(ctx, "router_kernel");
+    // larger batches: token tile staged in shared memory, one or two expert rows per warp
+    const size_t smem = (size_t)kTileTokens * c.hidden_size * sizeof(Tt);
+    const bool two = c.num_experts > 8;
+    auto k1 = router_tile_kernel<Tt, 1>;
+    auto k2 = router_tile_kernel<Tt, 2>;
+    auto k1n = router_tile_kernel<Tt, 1, true>;
+    auto k2n = router_tile_kernel<Tt, 2, true>;
+    static ConfiguredDevices configured;   // per template instance (one per element type)
+    if (configured.needs(c.device)) {
+      CUDA_TRY(ctx, cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      CUDA_TRY(ctx, cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      CUDA_TRY(ctx, cudaFuncSetAttribute(k1n, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      CUDA_TRY(ctx, cudaFuncSetAttribute(k2n, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      configured.done(c.device);
+    }
+    if (smem > 160 * 1024) return fail(ctx, B200MOE_E_UNSUPPORTED, "router: hidden size %d too large for the token tile", c.hidden_size);
+    const unsigned per_cta = 8u * (two ? 2u : 1u);
+    const dim3 grid((T + kTileTokens - 1) / kTileTokens, (c.num_experts + per_cta - 1) / per_cta);
+    if (with_norm) launch_chain(two ? k2n : k1n, grid, dim3(kRouterThreads), smem, st, p, *tab);
+    else launch_chain(two ? k2 : k1, grid, dim3(kRouterThreads), smem, st, p, *tab);
+    return post_launch(ctx, "router_tile_kernel");
   });
 }
 
@@ -524,6 +603,32 @@ extern "C" int b200moe_last_tables(b200moe_ctx* ctx, int T, int32_t* offsets_out
   return B200MOE_OK;
 }
 
+extern "C" int b200moe_group_pairs(b200moe_ctx* ctx, const int64_t* ids, int T, int32_t* tables_out, void* stream) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_group_pairs: null context");
+  int rc = check_tokens(ctx, T, "b200moe_group_pairs");
+  if (rc) return rc;
+  if (T == 0) return B200MOE_OK;
+  if (!ids || !tables_out) return fail(ctx, B200MOE_E_ARG, "b200moe_group_pairs: null pointer");
+  const b200moe_config& c = ctx->cfg;
+  CUDA_TRY(ctx, cudaSetDevice(c.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int E = c.num_experts;
+  SlotTable tab;
+  for (int e = 0; e < kMaxExperts; ++e) { tab.slot[e] = (int16_t)(e < E ? e : -1); tab.rank[e] = (uint8_t)(e & 255); }
+  PermuteParams pp{};
+  pp.ids64 = ids; pp.T = T; pp.K = c.top_k; pp.E = E;
+  pp.offsets = ctx->offsets; pp.sorted_pair = ctx->sorted_pair; pp.inv = ctx->inv;
+  pp.act_list = ctx->act_list; pp.n_act = ctx->n_act; pp.status = ctx->status;
+  pp.ep_cap = -1;                                    // ids outside [0,E) are dropped without a status bit, as the reference's `==` test drops them
+  const int pthreads = std::min(kPermuteMaxThreads, std::max(256, (T * c.top_k + 31) / 32 * 32));
+  const size_t smem = (size_t)((pthreads / 32) * E + E) * sizeof(int);
+  launch_chain(permute_kernel, dim3(1), dim3(pthreads), smem, st, pp, tab);
+  if ((rc = post_launch(ctx, "permute_kernel"))) return rc;
+  CUDA_TRY(ctx, cudaMemcpyAsync(tables_out, ctx->offsets, (size_t)(E + 1) * sizeof(int), cudaMemcpyDefault, st));
+  CUDA_TRY(ctx, cudaMemcpyAsync(tables_out + E + 1, ctx->sorted_pair, (size_t)T * c.top_k * sizeof(int), cudaMemcpyDefault, st));
+  return B200MOE_OK;
+}
+
 // ------------------------------------------------------------------------------------------
 // expert execution
 // ------------------------------------------------------------------------------------------
@@ -562,14 +667,6 @@ struct FfnLaunch {
   int n_tokens = 0;      // rows of x (only the int4 tcgen05 path needs it)
   int n_act_bound = 1;   // upper bound on the number of experts with work
   bool ksplit_ok = false;   // the consumer of y accepts fp32 K-slices (the combine kernel does)
-};
-
-// The opt-in dynamic shared-memory size is a property of a kernel ON ONE DEVICE: remember per template
-// instance which devices have been configured (one bit each), not just that some device was.
-struct ConfiguredDevices {
-  std::atomic<unsigned long long> mask{0};
-  bool needs(int device) const { return device < 0 || device >= 64 || !((mask.load(std::memory_order_acquire) >> device) & 1ull); }
-  void done(int device) { if (device >= 0 && device < 64) mask.fetch_or(1ull << device, std::memory_order_release); }
 };
 
 using GemvDefault = GemvShape<8, 2048, 3>;
@@ -796,9 +893,11 @@ static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st,
   });
 }
 
+// route_first: the ids / scores buffers are OUTPUTS of the router, which this call launches first (fused entry).
 static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const int64_t* ids, const void* scores,
                        int scores_dtype, const int32_t* expert_slot, const int32_t* order, const void* residual,
-                       void* out, int ffn_kind, cudaStream_t st) {
+                       void* out, int ffn_kind, cudaStream_t st, bool route_first = false, const void* route_x = nullptr,
+                       const RouterNorm* norm = nullptr) {
   const b200moe_config& c = ctx->cfg;
   const int E = c.num_experts;
   SlotTable tab;
@@ -820,13 +919,20 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   pp.ids64 = ids; pp.T = T; pp.K = c.top_k; pp.E = E;
   pp.offsets = ctx->offsets; pp.sorted_pair = ctx->sorted_pair; pp.inv = ctx->inv;
   pp.act_list = ctx->act_list; pp.n_act = ctx->n_act; pp.status = ctx->status;
-  const int pthreads = std::min(kPermuteMaxThreads, std::max(256, (T * c.top_k + 31) / 32 * 32));
-  const size_t smem = (size_t)((pthreads / 32) * E + E) * sizeof(int);
-  {
-    ProfScope prof(ctx, B200MOE_KERNEL_PERMUTE, st);
-    launch_chain(permute_kernel, dim3(1), dim3(pthreads), smem, st, pp, tab);
+  const bool fused_grouping = route_first && T * c.top_k <= kFusePermuteMaxPairs;
+  if (route_first &&
+      (rc = launch_router(ctx, layer, route_x ? route_x : x, nullptr, T, const_cast<int64_t*>(ids), const_cast<void*>(scores), nullptr, st,
+                          fused_grouping ? &pp : nullptr, &tab, norm)))
+    return rc;
+  if (!fused_grouping) {
+    const int pthreads = std::min(kPermuteMaxThreads, std::max(256, (T * c.top_k + 31) / 32 * 32));
+    const size_t smem = (size_t)((pthreads / 32) * E + E) * sizeof(int);
+    {
+      ProfScope prof(ctx, B200MOE_KERNEL_PERMUTE, st);
+      launch_chain(permute_kernel, dim3(1), dim3(pthreads), smem, st, pp, tab);
+    }
+    if ((rc = post_launch(ctx, "permute_kernel"))) return rc;
   }
-  if ((rc = post_launch(ctx, "permute_kernel"))) return rc;
 
   FfnLaunch f{};
   f.experts = ctx->d_experts + (size_t)layer * E;
@@ -900,8 +1006,31 @@ extern "C" int b200moe_forward_fused(b200moe_ctx* ctx, int layer, const void* x,
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int64_t* ids = ids_out ? ids_out : ctx->ids64;
   void* scores = scores_out ? scores_out : ctx->scores;
-  if ((rc = launch_router(ctx, layer, x, nullptr, T, ids, scores, nullptr, st))) return rc;
-  return run_experts(ctx, layer, x, T, ids, scores, ctx->cfg.act_dtype, nullptr, nullptr, residual, out, ffn_kind, st);
+  return run_experts(ctx, layer, x, T, ids, scores, ctx->cfg.act_dtype, nullptr, nullptr, residual, out, ffn_kind, st, true);
+}
+
+extern "C" int b200moe_forward_fused_norm(b200moe_ctx* ctx, int layer, const void* hidden, const void* residual, const void* norm_weight, float eps,
+                                          int T, void* out, void* residual_out, void* normed_out, int64_t* ids_out, void* scores_out, int ffn_kind,
+                                          void* stream) {
+  int rc = check_layer(ctx, layer, "b200moe_forward_fused_norm");
+  if (rc) return rc;
+  if ((rc = check_tokens(ctx, T, "b200moe_forward_fused_norm"))) return rc;
+  if (T == 0) return B200MOE_OK;
+  if (!hidden || !norm_weight || !out) return fail(ctx, B200MOE_E_ARG, "b200moe_forward_fused_norm: null pointer");
+  if (misaligned(hidden) || misaligned(norm_weight) || misaligned(out) || (residual && misaligned(residual)) || (residual_out && misaligned(residual_out)) ||
+      (normed_out && misaligned(normed_out)))
+    return fail(ctx, B200MOE_E_ARG, "b200moe_forward_fused_norm: pointers must be 16-byte aligned");
+  if (!ctx->gate_w[layer]) return fail(ctx, B200MOE_E_STATE, "b200moe_forward_fused_norm: no gate weight registered for layer %d", layer);
+  if (ffn_kind < B200MOE_FFN_AUTO || ffn_kind > B200MOE_FFN_MMA) return fail(ctx, B200MOE_E_ARG, "b200moe_forward_fused_norm: unknown ffn_kind %d", ffn_kind);
+  CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  RouterNorm nm;
+  nm.residual = residual; nm.weight = norm_weight; nm.eps = eps;
+  nm.normed_out = normed_out ? normed_out : ctx->xnorm;
+  nm.res_out = residual_out ? residual_out : ctx->xres;       // without an incoming residual this is a copy of `hidden`, the residual the block adds
+  int64_t* ids = ids_out ? ids_out : ctx->ids64;
+  void* scores = scores_out ? scores_out : ctx->scores;
+  return run_experts(ctx, layer, nm.normed_out, T, ids, scores, ctx->cfg.act_dtype, nullptr, nullptr, nm.res_out, out, ffn_kind, st, true, hidden, &nm);
 }
 
 // ------------------------------------------------------------------------------------------

@@ -295,13 +295,11 @@ template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine
   __shared__ int s_order[kMaxTopK];
   __shared__ int s_n;
   const int t = blockIdx.x;
-  pdl_wait();        // y comes from the down projection launched just before
   pdl_trigger();
-  const bool remote_y = p.wait_flags != nullptr;
-  if (remote_y && threadIdx.x >= 32 && threadIdx.x < 32 + p.n_wait) {
-    if (!ep_wait_flag(p.wait_flags + (threadIdx.x - 32), *p.epoch, p.wait_cycles)) atomicOr(p.status, kDevWaitExpired);
-  }
-  // slot k of the token is read by thread k; thread 0 then orders the live ones by rank
+  // The routing (ids, scores) and the inverse map were complete before the expert kernels could start (each of
+  // them passes its own dependency wait before it lets its successor launch), so this prologue may run while
+  // the down projection is still producing y: slot k of the token is read by thread k, thread 0 then orders
+  // the live ones by rank.
   if (threadIdx.x < p.K) {
     const int k = threadIdx.x;
     const long long e = p.ids64[(size_t)t * p.K + k];
@@ -328,6 +326,11 @@ template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine
       s_order[i] = k;
     }
     s_n = n;
+  }
+  pdl_wait();        // y comes from the down projection launched just before
+  const bool remote_y = p.wait_flags != nullptr;
+  if (remote_y && threadIdx.x >= 32 && threadIdx.x < 32 + p.n_wait) {
+    if (!ep_wait_flag(p.wait_flags + (threadIdx.x - 32), *p.epoch, p.wait_cycles)) atomicOr(p.status, kDevWaitExpired);
   }
   __syncthreads();
   const int n = s_n;

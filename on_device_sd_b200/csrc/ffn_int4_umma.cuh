@@ -12,7 +12,10 @@
 //      bytes in shared-memory traffic (write + read).
 //   -> tcgen05.mma with A from tensor memory and B (tokens) from shared memory, accumulator in
 //      tensor memory, epilogue as in ffn_umma.cuh.
-// Tensor memory (512 columns): accumulators 2 x PARTS x NMAX at column 0, A ring 4 x 64 columns at 256.
+// Tensor memory (512 columns): accumulators 2 x PARTS x NMAX at column 0, then the A ring of 64-column slots:
+// six slots for the 16-token tile (the accumulators take 128 columns there), four otherwise.  With more
+// slots than dequant groups a group does not have to wait for the MMAs of its own previous stage to
+// release "its" slot before it may store the next tile (measured: a third of a group's time).
 //
 // Token tiles also arrive by TMA: a small kernel first writes the tokens of every (token, expert)
 // pair in sorted-pair order - so an expert's rows are contiguous, like the rows of h - with the k
@@ -24,7 +27,7 @@
 //
 //   warp 0      TMA producer, weights   warp 2      TMA producer, tokens
 //   warps 1, 3  MMA issuers: issuer w takes the k-stages whose running index is w modulo 2 (warp 1 owns the TMEM allocation)
-//   warps 4-19  dequant: four groups of 4 warps; group g owns A stage g, i.e. every fourth k-stage,
+//   warps 4-19  dequant: four groups of 4 warps; group g takes every fourth k-stage (running index g modulo 4),
 //               thread = one weight row of the stage (64 bytes of nibbles -> 64 columns)
 //   warps 20-23 epilogue
 // Producer and issuer warps run warp-uniform with one elected lane per instruction (see tc_mma_bf16_w).
@@ -38,22 +41,21 @@
 
 namespace b200moe {
 
-constexpr int kI4uDeqGroups = 4;                  // = number of A stages: group g always fills stage g
+constexpr int kI4uDeqGroups = 4;                  // groups of dequant warps; group g takes the stages g modulo 4
 constexpr int kI4uDeqWarps = 4 * kI4uDeqGroups;   // per group: one warp per TMEM lane quarter
 constexpr int kI4uFirstDeq = 4;
 constexpr int kI4uFirstEpi = kI4uFirstDeq + kI4uDeqWarps;
 constexpr int kI4uThreads = (kI4uFirstEpi + 4) * 32;
 constexpr int kI4uWTile = 128 * 64;       // 128 rows x 64 bytes = 128 k of nibbles
 constexpr int kI4uBK = 128;
-constexpr int kI4uAStages = 4;            // dequantised A tiles in tensor memory
 constexpr int kI4uACols = 64;             // 128 k of bf16 = 64 32-bit columns per lane
-constexpr int kI4uACol0 = 256;            // first column of the A ring (accumulators sit below)
 
 // Shared memory: the packed-tile ring (the bytes in flight from HBM) and a ring of token tiles.
 template <int NMAX> struct I4uShape {
   static constexpr int B_TILE = 2 * NMAX * 128;                 // two 64-k atoms of NMAX rows x 128 bytes
   static constexpr int W_STAGES = NMAX <= 16 ? 20 : (NMAX == 32 ? 16 : (NMAX == 64 ? 12 : 8));   // 8 KB each; a multiple of the number of dequant groups
-  static constexpr int A_STAGES = kI4uAStages;
+  static constexpr int A_STAGES = NMAX <= 16 ? 6 : 4;           // dequantised A tiles in tensor memory
+  static constexpr int A_COL0 = 512 - A_STAGES * kI4uACols;     // first column of the A ring (accumulators sit below)
   // Successive MMAs into one accumulator serialise on its latency, so the k-steps rotate over
   // PARTS independent accumulators that the epilogue adds up.
   static constexpr int PARTS = NMAX <= 32 ? 4 : (NMAX == 64 ? 2 : 1);
@@ -68,12 +70,12 @@ template <int NMAX> struct I4uShape {
   static constexpr int MMA_WARPS = PARTS >= 2 ? 2 : 1;
   static constexpr int PARTS_PER_WARP = PARTS / MMA_WARPS;
   static constexpr int EX_BYTES = 64 * 17 * 4;
-  static constexpr int FIXED = 1024 + W_STAGES * kI4uWTile + EX_BYTES + 512;
+  static constexpr int FIXED = 1024 + W_STAGES * kI4uWTile + EX_BYTES + 1024;   // alignment slack, packed ring, epilogue exchange, barriers
   static constexpr int B_FIT = (227 * 1024 - FIXED) / B_TILE;
   static constexpr int B_STAGES = (B_FIT > 8 ? 8 : B_FIT) / MMA_WARPS * MMA_WARPS;
   static constexpr size_t SMEM = (size_t)FIXED + (size_t)B_STAGES * B_TILE;
   static constexpr int TMEM_COLS = 512;
-  static_assert(2 * PARTS * NMAX <= kI4uACol0, "accumulators overlap the A ring");
+  static_assert(2 * PARTS * NMAX <= A_COL0, "accumulators overlap the A ring");
   static_assert(B_STAGES >= 3 && A_STAGES % MMA_WARPS == 0 && B_STAGES % MMA_WARPS == 0, "ring depths");
 };
 
@@ -269,7 +271,7 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
               const bool got = wait_or_abort(&full[s], ph, abort_flag) && wait_or_abort(&b_full[sb], phb, abort_flag);
               if (!__all_sync(0xffffffffu, got)) { ok = false; break; }
               tc_fence_after();
-              const uint32_t a_tmem = tmem_base + (uint32_t)(kI4uACol0 + s * kI4uACols);
+              const uint32_t a_tmem = tmem_base + (uint32_t)(S::A_COL0 + s * kI4uACols);
 #pragma unroll
               for (int atom = 0; atom < 2; ++atom) {
                 const uint64_t bdesc = umma_desc_sw128(smem_addr(Bs + (size_t)sb * B_TILE + atom * NMAX * 128));
@@ -297,15 +299,16 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
     // ------------------------------ dequant: packed tile -> bf16 A tile in tensor memory ------------------------------
     // A warp may only touch the 32 TMEM lanes of its quarter (warp % 4): thread = weight row of the stage.
     // Group grp handles the k-stages whose running index is grp modulo 4 and therefore always A stage grp.
-    static_assert(kI4uDeqGroups == kI4uAStages && WSTAGES % kI4uDeqGroups == 0, "group <-> stage mapping");
+    // Group grp handles the k-stages whose running index gi (over the whole kernel) is grp modulo 4.  Stage gi
+    // lives in packed-ring slot gi % WSTAGES and goes to A slot gi % STAGES; the phase of a slot's barriers
+    // is the parity of how often the slot has been used, (gi / depth) & 1.
     const int q = warp & 3;
     const int row = q * 32 + lane, grp = (warp - kI4uFirstDeq) >> 2;
     const int sw = (row >> 1) & 3;              // 64-byte swizzle of the TMA box: 16-byte slot c of row r sits at c ^ ((r >> 1) & 3)
     const unsigned char* wrow0 = Ws + row * 64;
-    const uint32_t a_addr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(kI4uACol0 + grp * kI4uACols);
-    int ws = grp;                                 // packed-ring slot of this group's next stage
+    const uint32_t a_addr0 = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)S::A_COL0;
+    int gi = grp;                                 // running index of this group's next stage
     int first = grp;                              // first k-stage of the next job that belongs to this group
-    uint32_t wph = 0, ph = 0;
     bool ok = true;
     for (int item = blockIdx.x; item < total && ok; item += gridDim.x) {
       const int e = p.act_list[item / tiles];
@@ -324,8 +327,10 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
       for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
         int kb = first;
         __nv_bfloat16 sv = sc[min(kb, nkb - 1)];
-        for (; kb < nkb; kb += kI4uDeqGroups) {
+        for (; kb < nkb; kb += kI4uDeqGroups, gi += kI4uDeqGroups) {
           const __nv_bfloat16 sv_next = sc[min(kb + kI4uDeqGroups, nkb - 1)];   // the scale of this group's next stage is fetched a stage ahead
+          const int ws = gi % WSTAGES, as = gi % STAGES;
+          const uint32_t wph = (uint32_t)(gi / WSTAGES) & 1u, aph = (uint32_t)(gi / STAGES) & 1u;
           if (!__all_sync(0xffffffffu, wait_or_abort(&w_full[ws], wph, abort_flag))) { ok = false; break; }   // warp-uniform
           const unsigned char* wrow = wrow0 + (size_t)ws * kI4uWTile;
           uint4 pk[4];
@@ -333,9 +338,8 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
           for (int c = 0; c < 4; ++c) pk[c] = *reinterpret_cast<const uint4*>(wrow + ((c ^ sw) << 4));
           __syncwarp();
           if (lane == 0) mbar_arrive(&w_empty[ws]);
-          ws += kI4uDeqGroups;
-          if (ws >= WSTAGES) { ws -= WSTAGES; wph ^= 1; }
           const __nv_bfloat162 s2 = __nv_bfloat162(sv, sv);
+          const uint32_t a_addr = a_addr0 + (uint32_t)(as * kI4uACols);
           bool free_checked = false;
 #pragma unroll
           for (int half = 0; half < 2; ++half) {  // 64 k = 32 columns at a time keeps the register count down
@@ -349,7 +353,7 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
               o[4 * c + 0] = o4[0]; o[4 * c + 1] = o4[1]; o[4 * c + 2] = o4[2]; o[4 * c + 3] = o4[3];
             }
             if (!free_checked) {
-              if (!__all_sync(0xffffffffu, wait_or_abort(&empty[grp], ph ^ 1, abort_flag))) { ok = false; break; }
+              if (!__all_sync(0xffffffffu, wait_or_abort(&empty[as], aph ^ 1, abort_flag))) { ok = false; break; }
               tc_fence_after();
               free_checked = true;
             }
@@ -358,8 +362,7 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
           if (!ok) break;
           tc_wait_st();
           tc_fence_before();
-          if (lane == 0) mbar_arrive(&full[grp]);
-          ph ^= 1;
+          if (lane == 0) mbar_arrive(&full[as]);
           sv = sv_next;
         }
         first = kb - nkb;                         // the stride carries over into the next job

@@ -68,9 +68,10 @@ __device__ __forceinline__ int block_exclusive_scan_256(int v, int* warp_tot, in
   return base + inc - v;
 }
 
-// One CTA of 256..1024 threads (a multiple of 32, at least 256 so that every expert has a thread).
-static __global__ void __launch_bounds__(kPermuteMaxThreads) permute_kernel(PermuteParams p, SlotTable st) {
-  extern __shared__ int smem[];
+// The whole grouping, executed by ONE CTA of 256..1024 threads (a multiple of 32, at least 256 so that
+// every expert has a thread).  `smem` holds (blockDim/32 + 1) * E ints.  Called by permute_kernel and by
+// the tail of the router kernels (the CTA that finishes the last token tile groups the batch it just routed).
+__device__ __forceinline__ void permute_block(const PermuteParams& p, const SlotTable& st, int* smem) {
   const int nwarps = blockDim.x >> 5;
   int* cnt = smem;                  // [nwarps][E]
   int* offs = smem + nwarps * p.E;  // [E]
@@ -82,8 +83,6 @@ static __global__ void __launch_bounds__(kPermuteMaxThreads) permute_kernel(Perm
   const int begin = warp * per_warp, end = min(begin + per_warp, npairs);
 
   for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) cnt[i] = 0;
-  pdl_wait();        // ids come from the router launched just before
-  pdl_trigger();
   __shared__ int ep_cnt[8];
   if (p.ep_meta != nullptr) {
     if (threadIdx.x < p.ep_G) {
@@ -95,20 +94,21 @@ static __global__ void __launch_bounds__(kPermuteMaxThreads) permute_kernel(Perm
   __syncthreads();
   // id of pair pr: -1 = padding (skipped silently), anything else outside [0,E) is reported
   auto load_id = [&](int pr) -> long long {
-    if (p.ep_meta == nullptr) return p.ids64[pr];
+    if (p.ep_meta == nullptr) return __ldcg(reinterpret_cast<const long long*>(p.ids64) + pr);   // L2: another CTA of this grid may have written it
     const int s = pr / p.ep_cap, j = pr - s * p.ep_cap;
     if (j >= ep_cnt[s]) return -1;
     const int e = __ldcg(&p.ep_meta[pr]).x;
     return (e < 0) ? -2 : e;
   };
   const bool pad_ok = p.ep_meta != nullptr;
+  const bool quiet = p.ep_meta == nullptr && p.ep_cap < 0;      // grouping for a caller that only wants the tables: unknown ids are dropped silently
 
   for (int b = begin; b < end; b += 32) {
     const int pr = b + lane;
     if (pr < end) {
       const long long e = load_id(pr);
       if (e >= 0 && e < E) atomicAdd(&cnt[warp * E + (int)e], 1);
-      else if (!(pad_ok && e == -1)) atomicOr(p.status, kDevBadExpertId);
+      else if (!(pad_ok && e == -1) && !quiet) atomicOr(p.status, kDevBadExpertId);
     }
   }
   __syncthreads();
@@ -159,6 +159,13 @@ static __global__ void __launch_bounds__(kPermuteMaxThreads) permute_kernel(Perm
       }
     }
   }
+}
+
+static __global__ void __launch_bounds__(kPermuteMaxThreads) permute_kernel(PermuteParams p, SlotTable st) {
+  extern __shared__ int smem[];
+  pdl_wait();        // ids come from the router launched just before
+  pdl_trigger();
+  permute_block(p, st, smem);
 }
 
 }  // namespace b200moe

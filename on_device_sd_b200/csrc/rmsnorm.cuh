@@ -35,15 +35,14 @@ template <typename T> __device__ __forceinline__ void norm_store_chunk(T* dst, c
   }
 }
 
-template <typename T> __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(NormParams p) {
-  __shared__ float s_part[kNormThreads / 32];
-  __shared__ float s_scale;
-  pdl_wait();
-  pdl_trigger();
-  const int row = blockIdx.x;
-  const int nch = p.H / 8;
-  const T* x = reinterpret_cast<const T*>(p.x) + (size_t)row * p.H;
-  const T* res = p.residual ? reinterpret_cast<const T*>(p.residual) + (size_t)row * p.H : nullptr;
+// One row, executed by ALL kNormThreads threads of a CTA (it synchronises).  Destinations that are null are
+// skipped: out_a / out_b receive the normalised row (either may be shared memory), res_out the sum x + residual.
+// rmsnorm_kernel and the router kernels (norm fused into their load of the token) both call this, so the
+// fused form produces the same bits as the stand-alone one.
+template <typename T>
+__device__ __forceinline__ void rmsnorm_row(const T* x, const T* res, const T* w, float eps, int H, T* out_a, T* out_b, T* res_out,
+                                            float* s_part, float* s_scale) {
+  const int nch = H / 8;
   float v[kNormMaxChunks][8];
   float ss = 0.0f;
 #pragma unroll
@@ -60,8 +59,8 @@ template <typename T> __global__ void __launch_bounds__(kNormThreads) rmsnorm_ke
         rc.unpack(rf);
 #pragma unroll
         for (int i = 0; i < 8; ++i) v[j][i] = __fadd_rn(v[j][i], rf[i]);
-        if (p.residual_out) norm_store_chunk<T>(reinterpret_cast<T*>(p.residual_out) + (size_t)row * p.H + c * 8, v[j]);
       }
+      if (res_out) norm_store_chunk<T>(res_out + c * 8, v[j]);
 #pragma unroll
       for (int i = 0; i < 8; ++i) ss = fmaf(v[j][i], v[j][i], ss);
     }
@@ -72,14 +71,12 @@ template <typename T> __global__ void __launch_bounds__(kNormThreads) rmsnorm_ke
   if (threadIdx.x == 0) {
     float tot = 0.0f;
 #pragma unroll
-    for (int w = 0; w < kNormThreads / 32; ++w) tot += s_part[w];
-    const float var = __fdiv_rn(tot, (float)p.H);
-    s_scale = __frcp_rn(__fsqrt_rn(__fadd_rn(var, p.eps)));     // 1 / sqrt: the two correctly rounded steps of torch's CPU rsqrt
+    for (int wi = 0; wi < kNormThreads / 32; ++wi) tot += s_part[wi];
+    const float var = __fdiv_rn(tot, (float)H);
+    *s_scale = __frcp_rn(__fsqrt_rn(__fadd_rn(var, eps)));     // 1 / sqrt: the two correctly rounded steps of torch's CPU rsqrt
   }
   __syncthreads();
-  const float scale = s_scale;
-  const T* w = reinterpret_cast<const T*>(p.weight);
-  T* out = reinterpret_cast<T*>(p.out) + (size_t)row * p.H;
+  const float scale = *s_scale;
 #pragma unroll
   for (int j = 0; j < kNormMaxChunks; ++j) {
     const int c = threadIdx.x + j * kNormThreads;
@@ -90,9 +87,23 @@ template <typename T> __global__ void __launch_bounds__(kNormThreads) rmsnorm_ke
       wc.unpack(wf);
 #pragma unroll
       for (int i = 0; i < 8; ++i) o[i] = __fmul_rn(rn<T>(__fmul_rn(v[j][i], scale)), wf[i]);
-      norm_store_chunk<T>(out + c * 8, o);
+      if (out_a) norm_store_chunk<T>(out_a + c * 8, o);
+      if (out_b) norm_store_chunk<T>(out_b + c * 8, o);
     }
   }
+  __syncthreads();      // s_part / s_scale may be reused for the next row
+}
+
+template <typename T> __global__ void __launch_bounds__(kNormThreads) rmsnorm_kernel(NormParams p) {
+  __shared__ float s_part[kNormThreads / 32];
+  __shared__ float s_scale;
+  pdl_wait();
+  pdl_trigger();
+  const size_t row = blockIdx.x;
+  const T* res = p.residual ? reinterpret_cast<const T*>(p.residual) + row * p.H : nullptr;
+  T* res_out = (p.residual && p.residual_out) ? reinterpret_cast<T*>(p.residual_out) + row * p.H : nullptr;
+  rmsnorm_row<T>(reinterpret_cast<const T*>(p.x) + row * p.H, res, reinterpret_cast<const T*>(p.weight), p.eps, p.H,
+                 reinterpret_cast<T*>(p.out) + row * p.H, nullptr, res_out, s_part, &s_scale);
 }
 
 }  // namespace b200moe

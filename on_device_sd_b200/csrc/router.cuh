@@ -15,6 +15,8 @@
 #pragma once
 #include <type_traits>
 #include "common.cuh"
+#include "permute.cuh"
+#include "rmsnorm.cuh"
 
 namespace b200moe {
 
@@ -31,16 +33,55 @@ struct RouterParams {
   void* scores;         // [T,K] model dtype
   unsigned long long* bitmap;  // 4 words or null
   int T, H, E, K;
+  // Fused grouping: when fuse_permute is set, the CTA that finishes the LAST token tile of the grid runs
+  // the token-to-expert grouping (permute_block) over the ids the grid has just written, so the permute
+  // launch and its dependency edge disappear.  all_done counts finished tiles and returns to zero.
+  int fuse_permute;
+  unsigned* all_done;
+  PermuteParams perm;
+  // RMSNorm fused into the load of the tokens (NORM instances of the kernels): x is then the raw hidden state,
+  // s = x (+ norm_res), the routed row is T(T(s * rsqrt(mean(s^2) + eps)) * norm_w) - the reference's
+  // post_attention_layernorm (demo/src/layers/layernorm.py:21-36, call site demo/src/model/qwen3_runner.py:204).
+  // The CTAs of expert group 0 write the normalised rows to normed_out (read by the expert kernels) and
+  // T(s) to res_out (the residual the combine adds); either may be null.
+  const void* norm_res;
+  const void* norm_w;
+  void* normed_out;
+  void* res_out;
+  float norm_eps;
 };
 
-template <typename T> __device__ __forceinline__ double exact_dot(const T* xr, const T* wr, int nch, int lane) {
+constexpr int kRouterFuseSmemInts = (kRouterThreads / 32 + 1) * kMaxExperts;
+
+// Tail shared by the router kernels: called by every thread of a CTA that has just finished the top-k of a
+// token tile.  Returns after the grouping when this CTA was the last one of the grid.
+__device__ __forceinline__ void router_fused_tail(const RouterParams& p, const SlotTable& st, unsigned n_tiles, int* smem) {
+  __shared__ int s_all;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(p.all_done, 1u);
+    s_all = (prev == n_tiles - 1);
+    if (s_all) *p.all_done = 0u;
+  }
+  __syncthreads();
+  if (!s_all) return;
+  __threadfence();
+  permute_block(p.perm, st, smem);
+}
+
+// kSmemX: the token row lives in shared memory (tile kernel, fused norm), else in global memory.
+template <typename T, bool kSmemX = false> __device__ __forceinline__ double exact_dot(const T* xr, const T* wr, int nch, int lane) {
   double acc = 0.0;
   for (int c0 = lane; c0 < nch; c0 += 256) {
     Chunk<T> xc[8], wc[8];
 #pragma unroll
     for (int u = 0; u < 8; ++u) {
       const int c = c0 + 32 * u;
-      if (c < nch) { xc[u].template load<false>(xr + c * 8); wc[u].template load<false>(wr + c * 8); }
+      if (c < nch) {
+        if (kSmemX) xc[u].from_smem(xr + c * 8); else xc[u].template load<false>(xr + c * 8);
+        wc[u].template load<false>(wr + c * 8);
+      }
       else { xc[u].zero(); wc[u].zero(); }
     }
 #pragma unroll
@@ -174,7 +215,13 @@ __device__ void topk_softmax_token(const RouterParams& p, int t, int lane, float
 // The CTA that finishes a tile last runs phase 2 (top-k) for its tokens; the counter returns to
 // zero for the next call.  TT = 1 with 8 chunk positions per trip serves small batches
 // (latency-bound: every load of a row is in flight at once); TT = 4 amortises the weight row.
-template <typename T, int TT, int U> __global__ void __launch_bounds__(kRouterThreads) router_kernel(RouterParams p) {
+template <typename T, int TT, int U, bool NORM = false> __global__ void __launch_bounds__(kRouterThreads) router_kernel(RouterParams p, SlotTable st) {
+  static_assert(!NORM || TT == 1, "the fused norm stages one token row per CTA");
+  static_assert(kNormThreads == kRouterThreads, "rmsnorm_row is written for the router's CTA size");
+  extern __shared__ __align__(16) unsigned char xrow_raw[];       // NORM: the normalised row of this CTA's token
+  __shared__ float s_part[kNormThreads / 32];
+  __shared__ float s_scale;
+  __shared__ int s_perm[kRouterFuseSmemInts];
   constexpr bool kExact = std::is_same<T, float>::value;
   using Acc = typename std::conditional<kExact, double, float>::type;
   __shared__ float skey[TT][32];
@@ -188,6 +235,13 @@ template <typename T, int TT, int U> __global__ void __launch_bounds__(kRouterTh
   const T* bias = reinterpret_cast<const T*>(p.bias);
   pdl_wait();        // the previous call's combine may still read the ids / scores this kernel rewrites
   pdl_trigger();
+  if (NORM) {
+    const size_t off = (size_t)t0 * p.H;
+    const bool writer = blockIdx.y == 0;
+    rmsnorm_row<T>(x + off, p.norm_res ? reinterpret_cast<const T*>(p.norm_res) + off : nullptr, reinterpret_cast<const T*>(p.norm_w), p.norm_eps, p.H,
+                   reinterpret_cast<T*>(xrow_raw), (writer && p.normed_out) ? reinterpret_cast<T*>(p.normed_out) + off : nullptr,
+                   (writer && p.res_out) ? reinterpret_cast<T*>(p.res_out) + off : nullptr, s_part, &s_scale);
+  }
 
   if (e < p.E) {
     const T* wrow = reinterpret_cast<const T*>(p.wg) + (size_t)e * p.H;
@@ -207,8 +261,10 @@ template <typename T, int TT, int U> __global__ void __launch_bounds__(kRouterTh
         if (c < nch) {
           wc[u].template load<false>(wrow + c * 8);
 #pragma unroll
-          for (int tt = 0; tt < TT; ++tt)
-            xc[u][tt].template load<false>(x + (size_t)min(t0 + tt, p.T - 1) * p.H + c * 8);
+          for (int tt = 0; tt < TT; ++tt) {
+            if (NORM) xc[u][tt].from_smem(reinterpret_cast<const T*>(xrow_raw) + c * 8);
+            else xc[u][tt].template load<false>(x + (size_t)min(t0 + tt, p.T - 1) * p.H + c * 8);
+          }
         } else {
           wc[u].zero();
 #pragma unroll
@@ -244,7 +300,7 @@ template <typename T, int TT, int U> __global__ void __launch_bounds__(kRouterTh
         const float bound = cH * warp_sum(sabs[tt]) + 1e-37f;
         const bool risky = !(boundary_distance<T>(s) > bound);    // uniform: every lane holds the same sums
         if (risky && t0 + tt < p.T)
-          s = (float)exact_dot<T>(x + (size_t)(t0 + tt) * p.H, wrow, nch, lane);
+          s = (float)exact_dot<T, NORM>(NORM ? reinterpret_cast<const T*>(xrow_raw) : x + (size_t)(t0 + tt) * p.H, wrow, nch, lane);
       }
       float l = rn<T>(s);
       if (bias != nullptr) l = rn<T>(l + Elem<T>::to_float(bias[e]));
@@ -262,6 +318,122 @@ template <typename T, int TT, int U> __global__ void __launch_bounds__(kRouterTh
   if (!s_last) return;
   __threadfence();
   if (warp < TT && t0 + warp < p.T) topk_softmax_token<T>(p, t0 + warp, lane, skey[warp], sidx[warp]);
+  if (p.fuse_permute) router_fused_tail(p, st, gridDim.x, s_perm);
+}
+
+// Larger batches (T > 16): a CTA owns a tile of kTileTokens tokens x (8 * EPW) experts.  The token tile is
+// staged ONCE in shared memory and shared by the eight warps (the small-batch kernel lets every warp fetch
+// its tokens from L2 again, which is what bounded it); a warp streams EPW expert rows against all the
+// tile's tokens.  Same certificate as above with two accumulators per lane and (token, expert):
+// each sees at most H/64 + 1 roundings, then 1 + 5 for the pair and the warp tree.
+constexpr int kTileTokens = 8;
+template <typename T, int EPW, bool NORM = false> __global__ void __launch_bounds__(kRouterThreads) router_tile_kernel(RouterParams p, SlotTable st) {
+  __shared__ float s_part[kNormThreads / 32];
+  __shared__ float s_scale;
+  constexpr bool kExact = std::is_same<T, float>::value;
+  using Acc = typename std::conditional<kExact, double, float>::type;
+  constexpr int TT = kTileTokens;
+  extern __shared__ __align__(16) unsigned char tile_raw[];     // [TT][H] tokens of this tile
+  __shared__ float skey[TT][32];
+  __shared__ int sidx[TT][32];
+  __shared__ int s_last;
+  __shared__ int s_perm[kRouterFuseSmemInts];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int t0 = blockIdx.x * TT;
+  const int e0 = (blockIdx.y * (kRouterThreads / 32) + warp) * EPW;
+  const int nch = p.H / 8;
+  constexpr int CB = 8 * (int)sizeof(T);
+  const T* x = reinterpret_cast<const T*>(p.x);
+  const T* bias = reinterpret_cast<const T*>(p.bias);
+  pdl_wait();        // the previous call's combine may still read the ids / scores this kernel rewrites
+  pdl_trigger();
+  if (NORM) {
+    const bool writer = blockIdx.y == 0;
+    for (int tt = 0; tt < TT; ++tt) {
+      const int t = min(t0 + tt, p.T - 1);
+      const size_t off = (size_t)t * p.H;
+      const bool wr = writer && t0 + tt < p.T;
+      rmsnorm_row<T>(x + off, p.norm_res ? reinterpret_cast<const T*>(p.norm_res) + off : nullptr, reinterpret_cast<const T*>(p.norm_w), p.norm_eps, p.H,
+                     reinterpret_cast<T*>(tile_raw) + (size_t)tt * p.H, (wr && p.normed_out) ? reinterpret_cast<T*>(p.normed_out) + off : nullptr,
+                     (wr && p.res_out) ? reinterpret_cast<T*>(p.res_out) + off : nullptr, s_part, &s_scale);
+    }
+  } else {
+    for (int i = threadIdx.x; i < TT * nch; i += kRouterThreads) {
+      const int tt = i / nch, c = i - tt * nch;
+      Chunk<T> xc;
+      xc.template load<false>(x + (size_t)min(t0 + tt, p.T - 1) * p.H + c * 8);
+      if (sizeof(T) == 2) *reinterpret_cast<uint4*>(tile_raw + (size_t)i * CB) = *reinterpret_cast<const uint4*>(&xc);
+      else { reinterpret_cast<uint4*>(tile_raw + (size_t)i * CB)[0] = reinterpret_cast<const uint4*>(&xc)[0]; reinterpret_cast<uint4*>(tile_raw + (size_t)i * CB)[1] = reinterpret_cast<const uint4*>(&xc)[1]; }
+    }
+  }
+  __syncthreads();
+
+  if (e0 < p.E) {
+    const T* wrow[EPW];
+#pragma unroll
+    for (int ee = 0; ee < EPW; ++ee) wrow[ee] = reinterpret_cast<const T*>(p.wg) + (size_t)min(e0 + ee, p.E - 1) * p.H;
+    Acc acc[TT][EPW][2];
+    float sabs[TT][EPW];
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt)
+#pragma unroll
+      for (int ee = 0; ee < EPW; ++ee) { acc[tt][ee][0] = 0; acc[tt][ee][1] = 0; sabs[tt][ee] = 0.0f; }
+    for (int c = lane; c < nch; c += 32) {
+      float wf[EPW][8];
+#pragma unroll
+      for (int ee = 0; ee < EPW; ++ee) {
+        Chunk<T> wc;
+        wc.template load<false>(wrow[ee] + c * 8);
+        wc.unpack(wf[ee]);
+      }
+#pragma unroll
+      for (int tt = 0; tt < TT; ++tt) {
+        Chunk<T> xc;
+        xc.from_smem(tile_raw + ((size_t)tt * nch + c) * CB);
+        float xf[8];
+        xc.unpack(xf);
+#pragma unroll
+        for (int ee = 0; ee < EPW; ++ee)
+#pragma unroll
+          for (int i = 0; i < 8; ++i) {
+            if (kExact) {
+              acc[tt][ee][i & 1] = fma((double)xf[i], (double)wf[ee][i], acc[tt][ee][i & 1]);
+            } else {
+              acc[tt][ee][i & 1] = fmaf(xf[i], wf[ee][i], acc[tt][ee][i & 1]);
+              sabs[tt][ee] = fmaf(fabsf(xf[i]), fabsf(wf[ee][i]), sabs[tt][ee]);
+            }
+          }
+      }
+    }
+    const float cH = (float)(p.H / 64 + 12) * 5.9604645e-8f * 1.01f;
+#pragma unroll
+    for (int tt = 0; tt < TT; ++tt)
+#pragma unroll
+      for (int ee = 0; ee < EPW; ++ee) {
+        float s = (float)warp_sum(acc[tt][ee][0] + acc[tt][ee][1]);
+        const bool live = t0 + tt < p.T && e0 + ee < p.E;
+        if (!kExact) {
+          const float bound = cH * warp_sum(sabs[tt][ee]) + 1e-37f;
+          const bool risky = !(boundary_distance<T>(s) > bound);    // uniform: every lane holds the same sums
+          if (risky && live) s = (float)exact_dot<T, true>(reinterpret_cast<const T*>(tile_raw) + (size_t)tt * p.H, wrow[ee], nch, lane);
+        }
+        float l = rn<T>(s);
+        if (bias != nullptr && live) l = rn<T>(l + Elem<T>::to_float(bias[e0 + ee]));
+        if (lane == 0 && live) p.logits[(size_t)(t0 + tt) * p.E + e0 + ee] = l;
+      }
+  }
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(p.tile_counter + blockIdx.x, 1u);
+    s_last = (prev == gridDim.y - 1);
+    if (s_last) p.tile_counter[blockIdx.x] = 0;
+  }
+  __syncthreads();
+  if (!s_last) return;
+  __threadfence();
+  if (warp < TT && t0 + warp < p.T) topk_softmax_token<T>(p, t0 + warp, lane, skey[warp], sidx[warp]);
+  if (p.fuse_permute) router_fused_tail(p, st, gridDim.x, s_perm);
 }
 
 // Top-k / softmax on caller-supplied logits: one warp per token.

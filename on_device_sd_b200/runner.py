@@ -195,6 +195,11 @@ class B200MoERunner:
         self._last_layer = layer_idx
         return LazyRoutingResult(layer_idx, ids, scores, bitmap, ready, self.expert_id_cls)
 
+    def build_layer_activations(self, routing_result: Any):
+        """LayerExpertActivations of a routing (demo/src/execution/model_runner_utils.py:13-41) from the grouping kernel's tables."""
+        from .activations import build_layer_activations
+        return build_layer_activations(routing_result, self.config.num_experts, expert_id_cls=self.expert_id_cls, ctx=self.ctx)
+
     def forward_moe(self, layer_idx: int, attn_output: Any, expert_placement: Any) -> torch.Tensor:
         """residual + MoE(post_attn_normed); the add is fused into the combine kernel."""
         return self._execute_moe_with_placement(attn_output.post_attn_normed, expert_placement,

@@ -199,3 +199,35 @@ def test_moe_block_graph_replay_equals_eager_launches():
     for b in bufs:
         graphed.moe_block(0, b)
     assert len(graphed._graphs) == 2
+
+
+def test_layer_activations_from_the_grouping_kernel_equal_the_reference_loop():
+    """build_layer_activations fed by K2's tables (one device->host copy) against the oracle's restatement of the
+    reference's K x E torch.where loop, on CUDA tensors: random routing, duplicates, ids outside [0, E), the fixture."""
+    import numpy as np
+    from conftest import GOLDEN, from_np
+    from on_device_sd_b200 import B200MoERunner, MoEShape, RoutingResult
+    from test_host_logic import _check_activations
+    g = torch.Generator().manual_seed(13)
+    for T, K, E in [(1, 1, 4), (7, 2, 8), (64, 8, 128), (33, 4, 5), (256, 8, 128)]:
+        runner = B200MoERunner(MoEShape(64, E, K, 32, "bfloat16"), max_tokens=256)
+        ids = torch.stack([torch.randperm(E, generator=g)[:K] for _ in range(T)]).cuda()
+        scores = torch.rand(T, K, generator=g).to(torch.bfloat16).cuda()
+        acts = runner.build_layer_activations(RoutingResult(1, ids, scores, set()))
+        _check_activations(acts, O.layer_activations(ids.cpu(), scores.cpu(), E), 1, scores)
+        assert all(a.token_indices.is_cuda and a.scores.is_cuda for a in acts.activations)
+        assert runner.ctx.status() == 0
+    runner = B200MoERunner(MoEShape(64, 4, 2, 32, "bfloat16"), max_tokens=8)
+    ids = torch.tensor([[0, 0], [5, 1], [-1, 2], [2, 2]]).cuda()
+    scores = torch.rand(4, 2, generator=g).cuda()
+    _check_activations(runner.build_layer_activations(RoutingResult(0, ids, scores, set())), O.layer_activations(ids.cpu(), scores.cpu(), 4), 0, scores)
+    assert runner.ctx.status() == 0                       # unknown ids are dropped quietly here, as the reference's comparison drops them
+    z = np.load(GOLDEN / "activations_bf16.npz")
+    runner = B200MoERunner(MoEShape(64, int(z["num_experts"]), z["ids"].shape[1], 32, "bfloat16"), max_tokens=64)
+    ids = torch.from_numpy(z["ids"].astype(np.int64)).cuda()
+    scores = from_np(z["scores"], torch.bfloat16).cuda()
+    acts = runner.build_layer_activations(RoutingResult(3, ids, scores, set()))
+    cuts = np.r_[0, np.cumsum(z["count"])]
+    toks, asc = torch.from_numpy(z["tokens"].astype(np.int64)), from_np(z["act_scores"], torch.bfloat16)
+    want = [(int(k), int(e), toks[a:b], asc[a:b]) for k, e, a, b in zip(z["rank"], z["expert"], cuts[:-1], cuts[1:])]
+    _check_activations(acts, want, 3, scores)

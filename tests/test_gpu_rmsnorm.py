@@ -53,3 +53,40 @@ def test_rmsnorm_module_matches_oracle(T, H):
     want, want_res = O.rmsnorm(x, w, 1e-6, r)
     _ulp_close(out, want, torch.bfloat16)
     assert torch.equal(res.cpu(), want_res) and out.shape == x.shape
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+@pytest.mark.parametrize("T", [1, 5, 16, 17, 40])
+@pytest.mark.parametrize("with_residual", [True, False])
+def test_norm_fused_into_the_router_equals_norm_then_block(dtype, T, with_residual):
+    """b200moe_forward_fused_norm (the norm applied inside the router kernel's load of the tokens) against the
+    two-step form b200moe_rmsnorm -> b200moe_forward_fused: normalised rows, new residual, ids and output all
+    bit-identical, for the single-token-per-CTA router (T <= 16) and the tile router (T > 16)."""
+    from on_device_sd_b200 import MoEContext
+    from on_device_sd_b200.synth import make_layer
+    H, E, K, I = 256, 16, 4, 128
+    L = make_layer(H, E, K, I, dtype, T, seed=61)
+    ctx = MoEContext(H, E, K, I, dtype, max_tokens=64)
+    ctx.set_gate(0, L.gate_w.cuda())
+    for e, p in L.experts.items():
+        ctx.set_expert(0, e, {k: v.cuda() for k, v in p.items()})
+    g = torch.Generator().manual_seed(T)
+    hidden = (L.x * 3).to(dtype).cuda()
+    res = torch.randn(T, H, generator=g).to(dtype).cuda() if with_residual else None
+    w = (1.0 + 0.1 * torch.randn(H, generator=g)).to(dtype).cuda()
+    if with_residual:
+        normed, new_res = ctx.rmsnorm(hidden, w, 1e-6, res)
+    else:
+        normed, new_res = ctx.rmsnorm(hidden, w, 1e-6), hidden
+    want, want_ids, want_scores = ctx.forward_fused(0, normed, residual=new_res, return_routing=True)
+    out, r_out, n_out, ids, scores = ctx.forward_fused_norm(0, hidden, w, 1e-6, residual=res, return_parts=True)
+    assert ctx.status() == 0
+    assert torch.equal(n_out, normed) and torch.equal(r_out, new_res)
+    assert torch.equal(ids, want_ids) and torch.equal(scores, want_scores)
+    assert torch.equal(out, want)
+    assert torch.equal(ctx.forward_fused_norm(0, hidden, w, 1e-6, residual=res), want)      # internal buffers for the parts
+    # and against the oracle's norm + block
+    o_norm = O.rmsnorm(hidden.cpu(), w.cpu(), 1e-6, res.cpu() if with_residual else None)
+    o_n, o_r = o_norm if with_residual else (o_norm, hidden.cpu())
+    assert torch.equal(r_out.cpu(), o_r)
+    assert float((n_out.cpu().float() - o_n.float()).abs().max()) <= (1e-6 if dtype == torch.float32 else 2.0 ** -6)
