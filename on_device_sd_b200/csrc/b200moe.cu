@@ -520,26 +520,22 @@ static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void*
       }
       return post_launch(ctx, "router_kernel");
     }
-    // larger batches: token tile staged in shared memory, one or two expert rows per warp
+    // larger batches: token tile staged in shared memory, one expert row per warp
     const size_t smem = (size_t)kTileTokens * c.hidden_size * sizeof(Tt);
-    const bool two = c.num_experts > 8;
-    auto k1 = router_tile_kernel<Tt, 1>;
-    auto k2 = router_tile_kernel<Tt, 2>;
-    auto k1n = router_tile_kernel<Tt, 1, true>;
-    auto k2n = router_tile_kernel<Tt, 2, true>;
+    auto k1 = router_tile_kernel<Tt, kTileTokens, 1>;
+    auto k1n = router_tile_kernel<Tt, kTileTokens, 1, true>;
     static ConfiguredDevices configured;   // per template instance (one per element type)
     if (configured.needs(c.device)) {
       CUDA_TRY(ctx, cudaFuncSetAttribute(k1, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-      CUDA_TRY(ctx, cudaFuncSetAttribute(k2, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
       CUDA_TRY(ctx, cudaFuncSetAttribute(k1n, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
-      CUDA_TRY(ctx, cudaFuncSetAttribute(k2n, cudaFuncAttributeMaxDynamicSharedMemorySize, 160 * 1024));
+      // several CTAs per SM: ask for the shared-memory end of the L1 / shared split
+      CUDA_TRY(ctx, cudaFuncSetAttribute(k1, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
+      CUDA_TRY(ctx, cudaFuncSetAttribute(k1n, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared));
       configured.done(c.device);
     }
     if (smem > 160 * 1024) return fail(ctx, B200MOE_E_UNSUPPORTED, "router: hidden size %d too large for the token tile", c.hidden_size);
-    const unsigned per_cta = 8u * (two ? 2u : 1u);
-    const dim3 grid((T + kTileTokens - 1) / kTileTokens, (c.num_experts + per_cta - 1) / per_cta);
-    if (with_norm) launch_chain(two ? k2n : k1n, grid, dim3(kRouterThreads), smem, st, p, *tab);
-    else launch_chain(two ? k2 : k1, grid, dim3(kRouterThreads), smem, st, p, *tab);
+    const dim3 grid((T + kTileTokens - 1) / kTileTokens, (c.num_experts + 7) / 8);
+    launch_chain(with_norm ? k1n : k1, grid, dim3(kRouterThreads), smem, st, p, *tab);
     return post_launch(ctx, "router_tile_kernel");
   });
 }

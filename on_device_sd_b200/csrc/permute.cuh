@@ -26,9 +26,9 @@ struct PermuteParams {
   int* n_act;        // [1]
   int* status;
   // Expert-parallel source (ep_meta != null): the "pairs" are the rows of this rank's receive buffer,
-  // [ep_G][ep_cap] with K = 1; row j of source s holds expert ep_meta[s*cap+j].x when j < ep_count[s] and is
-  // padding otherwise.  The kernel first waits (bounded) until every source's dispatch flag has reached
-  // *ep_epoch.
+  // [ep_G][ep_cap] with K = 1; row j of source s holds expert ep_meta[s*cap+j].x when j < ep_count[s], the
+  // rest of a region is not visited (its inv entries keep whatever they held).  The kernel first waits
+  // (bounded) until every source's dispatch flag has reached *ep_epoch.
   const int2* ep_meta;
   const int* ep_count;
   const unsigned* ep_flags;
@@ -77,38 +77,50 @@ __device__ __forceinline__ void permute_block(const PermuteParams& p, const Slot
   int* offs = smem + nwarps * p.E;  // [E]
   __shared__ int warp_tot[8];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int E = p.E, npairs = p.T * p.K;
-  // contiguous, 32-aligned slice of the pair list per warp
-  const int per_warp = ((npairs + nwarps - 1) / nwarps + 31) / 32 * 32;
-  const int begin = warp * per_warp, end = min(begin + per_warp, npairs);
-
+  const int E = p.E;
   for (int i = threadIdx.x; i < nwarps * E; i += blockDim.x) cnt[i] = 0;
-  __shared__ int ep_cnt[8];
+  // Expert-parallel source: only the rows the sources really sent are visited.  ep_start[s] is the number of
+  // rows of the sources before s; visit index i in [ep_start[s], ep_start[s+1]) is row s*cap + (i - ep_start[s]).
+  __shared__ int ep_start[9];
   if (p.ep_meta != nullptr) {
     if (threadIdx.x < p.ep_G) {
       const bool ok = ep_wait_flag(p.ep_flags + threadIdx.x, *p.ep_epoch, p.ep_wait_cycles);
       if (!ok) atomicOr(p.status, kDevWaitExpired);
-      ep_cnt[threadIdx.x] = ok ? max(0, min(__ldcg(p.ep_count + threadIdx.x), p.ep_cap)) : 0;
+      ep_start[threadIdx.x + 1] = ok ? max(0, min(__ldcg(p.ep_count + threadIdx.x), p.ep_cap)) : 0;
+    }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+      ep_start[0] = 0;
+      for (int s = 0; s < p.ep_G; ++s) ep_start[s + 1] += ep_start[s];
     }
   }
   __syncthreads();
-  // id of pair pr: -1 = padding (skipped silently), anything else outside [0,E) is reported
+  const int npairs = p.ep_meta != nullptr ? ep_start[p.ep_G] : p.T * p.K;     // pairs to visit
+  // contiguous, 32-aligned slice of the visit list per warp
+  const int per_warp = ((npairs + nwarps - 1) / nwarps + 31) / 32 * 32;
+  const int begin = warp * per_warp, end = min(begin + per_warp, npairs);
+  // visit index -> pair index (row of the receive buffer in expert-parallel mode)
+  auto pair_of = [&](int i) -> int {
+    if (p.ep_meta == nullptr) return i;
+    int s = 0;
+#pragma unroll
+    for (int k = 1; k < 8; ++k) s += (k < p.ep_G && i >= ep_start[k]) ? 1 : 0;
+    return s * p.ep_cap + (i - ep_start[s]);
+  };
+  // id of pair pr: anything outside [0,E) is reported (or dropped quietly for a caller that only wants the tables)
   auto load_id = [&](int pr) -> long long {
     if (p.ep_meta == nullptr) return __ldcg(reinterpret_cast<const long long*>(p.ids64) + pr);   // L2: another CTA of this grid may have written it
-    const int s = pr / p.ep_cap, j = pr - s * p.ep_cap;
-    if (j >= ep_cnt[s]) return -1;
     const int e = __ldcg(&p.ep_meta[pr]).x;
     return (e < 0) ? -2 : e;
   };
-  const bool pad_ok = p.ep_meta != nullptr;
-  const bool quiet = p.ep_meta == nullptr && p.ep_cap < 0;      // grouping for a caller that only wants the tables: unknown ids are dropped silently
+  const bool quiet = p.ep_meta == nullptr && p.ep_cap < 0;
 
   for (int b = begin; b < end; b += 32) {
-    const int pr = b + lane;
-    if (pr < end) {
-      const long long e = load_id(pr);
+    const int vi = b + lane;
+    if (vi < end) {
+      const long long e = load_id(pair_of(vi));
       if (e >= 0 && e < E) atomicAdd(&cnt[warp * E + (int)e], 1);
-      else if (!(pad_ok && e == -1) && !quiet) atomicOr(p.status, kDevBadExpertId);
+      else if (!quiet) atomicOr(p.status, kDevBadExpertId);
     }
   }
   __syncthreads();
@@ -137,10 +149,13 @@ __device__ __forceinline__ void permute_block(const PermuteParams& p, const Slot
   }
   __syncthreads();
 
+  const int cap_pairs = p.T * p.K;      // size of the tables
   for (int b = begin; b < end; b += 32) {
-    const int pr = b + lane;
+    const int vi = b + lane;
+    int pr = -1;
     long long e = -1;
-    if (pr < end) {
+    if (vi < end) {
+      pr = pair_of(vi);
       e = load_id(pr);
       if (e < 0 || e >= E) e = -1;
     }
@@ -151,10 +166,10 @@ __device__ __forceinline__ void permute_block(const PermuteParams& p, const Slot
     __syncwarp();
     if (e >= 0 && rank == 0) cnt[warp * E + (int)e] += __popc(m);
     __syncwarp();
-    if (pr < end) {
+    if (vi < end) {
       p.inv[pr] = pos;
       if (pos >= 0) {
-        if (pos < npairs) p.sorted_pair[pos] = pr;
+        if (pos < cap_pairs) p.sorted_pair[pos] = pr;
         else atomicOr(p.status, kDevBadOffsets);
       }
     }

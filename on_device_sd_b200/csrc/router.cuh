@@ -321,18 +321,19 @@ template <typename T, int TT, int U, bool NORM = false> __global__ void __launch
   if (p.fuse_permute) router_fused_tail(p, st, gridDim.x, s_perm);
 }
 
-// Larger batches (T > 16): a CTA owns a tile of kTileTokens tokens x (8 * EPW) experts.  The token tile is
-// staged ONCE in shared memory and shared by the eight warps (the small-batch kernel lets every warp fetch
-// its tokens from L2 again, which is what bounded it); a warp streams EPW expert rows against all the
-// tile's tokens.  Same certificate as above with two accumulators per lane and (token, expert):
-// each sees at most H/64 + 1 roundings, then 1 + 5 for the pair and the warp tree.
-constexpr int kTileTokens = 8;
-template <typename T, int EPW, bool NORM = false> __global__ void __launch_bounds__(kRouterThreads) router_tile_kernel(RouterParams p, SlotTable st) {
+// Larger batches (T > 16): a CTA owns a tile of TT tokens x (8 * EPW) experts.  The token tile is staged
+// ONCE in shared memory and shared by the eight warps (letting every warp fetch its tokens from L2 again
+// made the kernel L2-bound); a warp streams EPW expert rows against all the tile's tokens.  Same
+// certificate as above with two accumulators per lane and (token, expert): each sees at most H/64 + 1
+// roundings, then 1 + 5 for the pair and the warp tree.  Small tiles (4 tokens x 8 experts) keep a CTA's
+// serial chain short - a warp reduces TT * EPW sums one after the other - and give the grid enough CTAs.
+constexpr int kTileTokens = 4;
+template <typename T, int TT, int EPW, bool NORM = false> __global__ void __launch_bounds__(kRouterThreads) router_tile_kernel(RouterParams p, SlotTable st) {
   __shared__ float s_part[kNormThreads / 32];
   __shared__ float s_scale;
   constexpr bool kExact = std::is_same<T, float>::value;
   using Acc = typename std::conditional<kExact, double, float>::type;
-  constexpr int TT = kTileTokens;
+  static_assert(TT <= kRouterThreads / 32, "one warp per token in the top-k phase");
   extern __shared__ __align__(16) unsigned char tile_raw[];     // [TT][H] tokens of this tile
   __shared__ float skey[TT][32];
   __shared__ int sidx[TT][32];
@@ -358,12 +359,25 @@ template <typename T, int EPW, bool NORM = false> __global__ void __launch_bound
                      (wr && p.res_out) ? reinterpret_cast<T*>(p.res_out) + off : nullptr, s_part, &s_scale);
     }
   } else {
-    for (int i = threadIdx.x; i < TT * nch; i += kRouterThreads) {
-      const int tt = i / nch, c = i - tt * nch;
-      Chunk<T> xc;
-      xc.template load<false>(x + (size_t)min(t0 + tt, p.T - 1) * p.H + c * 8);
-      if (sizeof(T) == 2) *reinterpret_cast<uint4*>(tile_raw + (size_t)i * CB) = *reinterpret_cast<const uint4*>(&xc);
-      else { reinterpret_cast<uint4*>(tile_raw + (size_t)i * CB)[0] = reinterpret_cast<const uint4*>(&xc)[0]; reinterpret_cast<uint4*>(tile_raw + (size_t)i * CB)[1] = reinterpret_cast<const uint4*>(&xc)[1]; }
+    constexpr int US = 4;                  // staging loads in flight per thread
+    for (int i0 = threadIdx.x; i0 < TT * nch; i0 += kRouterThreads * US) {
+      Chunk<T> xc[US];
+#pragma unroll
+      for (int u = 0; u < US; ++u) {
+        const int i = i0 + u * kRouterThreads;
+        if (i < TT * nch) {
+          const int tt = i / nch, c = i - tt * nch;
+          xc[u].template load<false>(x + (size_t)min(t0 + tt, p.T - 1) * p.H + c * 8);
+        }
+      }
+#pragma unroll
+      for (int u = 0; u < US; ++u) {
+        const int i = i0 + u * kRouterThreads;
+        if (i < TT * nch) {
+          if (sizeof(T) == 2) *reinterpret_cast<uint4*>(tile_raw + (size_t)i * CB) = *reinterpret_cast<const uint4*>(&xc[u]);
+          else { reinterpret_cast<uint4*>(tile_raw + (size_t)i * CB)[0] = reinterpret_cast<const uint4*>(&xc[u])[0]; reinterpret_cast<uint4*>(tile_raw + (size_t)i * CB)[1] = reinterpret_cast<const uint4*>(&xc[u])[1]; }
+        }
+      }
     }
   }
   __syncthreads();
@@ -378,31 +392,41 @@ template <typename T, int EPW, bool NORM = false> __global__ void __launch_bound
     for (int tt = 0; tt < TT; ++tt)
 #pragma unroll
       for (int ee = 0; ee < EPW; ++ee) { acc[tt][ee][0] = 0; acc[tt][ee][1] = 0; sabs[tt][ee] = 0.0f; }
-    for (int c = lane; c < nch; c += 32) {
-      float wf[EPW][8];
+    constexpr int UW = 4;                  // chunk positions per trip: their weight loads are all in flight before the first is used
+    for (int c0 = lane; c0 < nch; c0 += 32 * UW) {
+      Chunk<T> wc[UW][EPW];
 #pragma unroll
-      for (int ee = 0; ee < EPW; ++ee) {
-        Chunk<T> wc;
-        wc.template load<false>(wrow[ee] + c * 8);
-        wc.unpack(wf[ee]);
-      }
+      for (int u = 0; u < UW; ++u)
 #pragma unroll
-      for (int tt = 0; tt < TT; ++tt) {
-        Chunk<T> xc;
-        xc.from_smem(tile_raw + ((size_t)tt * nch + c) * CB);
-        float xf[8];
-        xc.unpack(xf);
+        for (int ee = 0; ee < EPW; ++ee) {
+          if (c0 + 32 * u < nch) wc[u][ee].template load<false>(wrow[ee] + (c0 + 32 * u) * 8);
+          else wc[u][ee].zero();
+        }
 #pragma unroll
-        for (int ee = 0; ee < EPW; ++ee)
+      for (int u = 0; u < UW; ++u) {
+        const int c = c0 + 32 * u;
+        if (c >= nch) break;
+        float wf[EPW][8];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) {
-            if (kExact) {
-              acc[tt][ee][i & 1] = fma((double)xf[i], (double)wf[ee][i], acc[tt][ee][i & 1]);
-            } else {
-              acc[tt][ee][i & 1] = fmaf(xf[i], wf[ee][i], acc[tt][ee][i & 1]);
-              sabs[tt][ee] = fmaf(fabsf(xf[i]), fabsf(wf[ee][i]), sabs[tt][ee]);
+        for (int ee = 0; ee < EPW; ++ee) wc[u][ee].unpack(wf[ee]);
+#pragma unroll
+        for (int tt = 0; tt < TT; ++tt) {
+          Chunk<T> xc;
+          xc.from_smem(tile_raw + ((size_t)tt * nch + c) * CB);
+          float xf[8];
+          xc.unpack(xf);
+#pragma unroll
+          for (int ee = 0; ee < EPW; ++ee)
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              if (kExact) {
+                acc[tt][ee][i & 1] = fma((double)xf[i], (double)wf[ee][i], acc[tt][ee][i & 1]);
+              } else {
+                acc[tt][ee][i & 1] = fmaf(xf[i], wf[ee][i], acc[tt][ee][i & 1]);
+                sabs[tt][ee] = fmaf(fabsf(xf[i]), fabsf(wf[ee][i]), sabs[tt][ee]);
+              }
             }
-          }
+        }
       }
     }
     const float cH = (float)(p.H / 64 + 12) * 5.9604645e-8f * 1.01f;

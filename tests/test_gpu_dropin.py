@@ -231,3 +231,54 @@ def test_layer_activations_from_the_grouping_kernel_equal_the_reference_loop():
     toks, asc = torch.from_numpy(z["tokens"].astype(np.int64)), from_np(z["act_scores"], torch.bfloat16)
     want = [(int(k), int(e), toks[a:b], asc[a:b]) for k, e, a, b in zip(z["rank"], z["expert"], cuts[:-1], cuts[1:])]
     _check_activations(acts, want, 3, scores)
+
+
+def test_runner_subclass_of_the_integration_note_runs_the_engine_sequence():
+    """The subclass a maintainer adds to the reference (the class body is the one shown in the integration
+    note), on a stand-in for Qwen3ModelRunner that has the same constructor arguments and attributes: per layer
+    route_experts -> placement from the loader's per-expert dicts -> forward_moe, as the engine loop does
+    (demo/src/execution/cb_executor.py:427-448)."""
+    import types
+    from on_device_sd_b200 import AttentionOutput, B200MoERunner, ExpertID, ExpertPlacement, MoEShape
+    from on_device_sd_b200.synth import make_layer
+
+    class Qwen3ModelRunnerStandIn:                      # constructor and attributes of demo/src/model/qwen3_runner.py:28-69
+        def __init__(self, config, parameter_loader):
+            self.config, self.parameter_loader, self.device = config, parameter_loader, torch.device("cuda")
+
+    class B200Qwen3ModelRunner(Qwen3ModelRunnerStandIn):
+        def __init__(self, config, parameter_loader, max_tokens=512):
+            super().__init__(config, parameter_loader)
+            self._moe = B200MoERunner(config, device=self.device, max_tokens=max_tokens, expert_id_cls=ExpertID)
+            for i in range(config.num_hidden_layers):
+                self._moe.load_gate(i, parameter_loader.static_params_gpu[f"layer_{i}.router"])
+
+        def route_experts(self, layer_idx, hidden_states):
+            return self._moe.route_experts(layer_idx, hidden_states)
+
+        def forward_moe(self, layer_idx, attn_output, expert_placement):
+            return self._moe.forward_moe(layer_idx, attn_output, expert_placement)
+
+        def _execute_moe_with_placement(self, hidden_states, expert_placement):
+            return self._moe._execute_moe_with_placement(hidden_states, expert_placement)
+
+    H, E, K, I, T, Ln = 128, 8, 2, 64, 10, 2
+    layers = [make_layer(H, E, K, I, torch.bfloat16, T, seed=70 + l, device="cuda") for l in range(Ln)]
+    loader = types.SimpleNamespace(static_params_gpu={f"layer_{l}.router": layers[l].gate_w for l in range(Ln)},
+                                   expert_params_gpu={ExpertID(l, e): layers[l].experts[e] for l in range(Ln) for e in range(E)})
+    runner = B200Qwen3ModelRunner(MoEShape(H, E, K, I, "bfloat16", num_hidden_layers=Ln), loader, max_tokens=16)
+    hidden = layers[0].x.view(1, T, H)
+    for step in range(2):                               # the second pass reuses the registered experts (same dict objects)
+        h = hidden
+        for l in range(Ln):
+            routing = runner.route_experts(l, h)
+            gpu = {eid.expert_idx: loader.expert_params_gpu[eid] for eid in routing.activated_expert_ids}
+            placement = ExpertPlacement(gpu_expert_params=gpu, cpu_expert_params={}, routing_result=routing)
+            out = runner.forward_moe(l, AttentionOutput(h, h, h), placement)
+            cpu = {e: {k: v.cpu() for k, v in p.items()} for e, p in layers[l].experts.items()}
+            ids, scores, _ = O.route(h.view(T, H).cpu(), layers[l].gate_w.cpu(), K)
+            assert torch.equal(routing.topk_indices.cpu(), ids)
+            want = O.moe_engine(h.view(T, H).cpu(), ids, scores, cpu, layer_idx=l, residual=h.view(T, H).cpu())
+            assert O.mean_rel(out.view(T, H).cpu(), want) <= 1e-3 and O.max_abs(out.view(T, H).cpu(), want) <= 2e-2
+            h = out
+    assert runner._moe.ctx.status() == 0

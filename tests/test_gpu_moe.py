@@ -23,7 +23,7 @@ def _register(ctx, experts, layer=0):
     return dev
 
 
-def _close(got, want, dtype, tight=False):
+def _close(got, want, dtype, tight=False, mean_rel_tol=None):
     """max-abs <= 2e-2 and mean-rel <= 5e-3 for 16-bit outputs (1e-5 for fp32).  The absolute bound
     is widened by two units in the last place of the expected value (2 * 2^-7 |y| for bf16,
     2 * 2^-10 |y| for fp16): with N(0, 0.02) weights the Mixtral-shaped layer produces |y| up to ~16,
@@ -34,6 +34,8 @@ def _close(got, want, dtype, tight=False):
     tol_a, tol_r = OUT_TOL[dtype]
     if tight and dtype != torch.float32:
         tol_r = 1e-3     # same rounding points and same accumulation order: far inside the budget
+    if mean_rel_tol is not None:
+        tol_r = mean_rel_tol
     ulp = {torch.float32: 0.0, torch.float16: 2.0 ** -9, torch.bfloat16: 2.0 ** -6}[dtype]
     if not got.numel():
         return ma, mr
