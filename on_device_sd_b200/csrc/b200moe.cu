@@ -88,7 +88,7 @@ struct b200moe_ctx {
     EpPeers peers{};
     unsigned char* base = nullptr;
     size_t bytes = 0;
-    unsigned* counters = nullptr;      // [0] epoch, [1] dispatch arrivals, [2] return arrivals
+    unsigned* counters = nullptr;      // [0] epoch, [1] dispatch arrivals, [2] return arrivals, [8..15] rows sent per destination
     long long wait_cycles = 1ll << 31; // about one second
     std::vector<void*> opened;         // IPC mappings to close
     int last_T_local = 0;
@@ -273,7 +273,7 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
     }
     if (cfg->weight_mode == B200MOE_W_DENSE) {
       const size_t slice = pairs * (size_t)H * sizeof(float);
-      int slices = (int)std::min<size_t>(8, (64u << 20) / std::max<size_t>(slice, 1));
+      int slices = (int)std::min<size_t>(12, (64u << 20) / std::max<size_t>(slice, 1));
       if (slices >= 2 && dev_alloc(ctx, &ctx->ypart, (size_t)slices * pairs * H) == B200MOE_OK) ctx->ypart_slices = slices;
     }
     cudaDriverEntryPointQueryResult qres;
@@ -741,9 +741,19 @@ static int launch_ffn_umma(b200moe_ctx* ctx, const FfnParams& p, const void* tma
   if (ksplit_ok && ctx->ypart_slices >= 2) {
     const int tiles = (p.H + 127) / 128, nkb = (p.I + 63) / 64;
     const int items = std::max(1, n_act_bound * tiles);
-    int ks = (8 * ctx->sm_count + items - 1) / items;
-    ks = std::min(std::min(ks, ctx->ypart_slices), std::max(1, nkb / 16));   // a slice keeps >= 16 k-blocks (1024 of K)
-    up.ksplit = std::max(1, ks);
+    int want = (8 * ctx->sm_count + items - 1) / items;
+    const int cap = std::min(std::min(want, ctx->ypart_slices), std::max(1, nkb / 16));   // a slice keeps >= 16 k-blocks (1024 of K)
+    // Among the allowed splits take the one whose work items fill whole rounds of the grid best: the items
+    // are equal-sized, so the launch lasts ceil(items * ks / SMs) rounds whatever the last round holds.
+    int best = 1;
+    double best_eff = 0.0;
+    for (int ks = std::max(1, cap / 2); ks <= cap; ++ks) {
+      const long long n = (long long)items * ks;
+      const long long rounds = (n + ctx->sm_count - 1) / ctx->sm_count;
+      const double eff = (double)n / (double)(rounds * ctx->sm_count);
+      if (eff > best_eff + 1e-9) { best_eff = eff; best = ks; }
+    }
+    up.ksplit = std::max(1, best);
   }
   ctx->last_ksplit = up.ksplit;
   if (ctx->cfg.act_dtype == B200MOE_F16) {
@@ -1059,10 +1069,10 @@ extern "C" int b200moe_ep_create(b200moe_ctx* ctx, int world, int rank, int max_
   cudaError_t e = cudaMalloc(&base, bytes);
   if (e != cudaSuccess) return fail(ctx, B200MOE_E_CUDA, "b200moe_ep_create: cudaMalloc(%zu bytes) failed: %s", bytes, cudaGetErrorString(e));
   ctx->allocs.push_back(base);
-  int rc = dev_alloc(ctx, &ep.counters, 4);
+  int rc = dev_alloc(ctx, &ep.counters, 16);
   if (rc) return rc;
   CUDA_TRY(ctx, cudaMemset(base, 0, bytes));
-  CUDA_TRY(ctx, cudaMemset(ep.counters, 0, 4 * sizeof(unsigned)));
+  CUDA_TRY(ctx, cudaMemset(ep.counters, 0, 16 * sizeof(unsigned)));
   CUDA_TRY(ctx, cudaDeviceSynchronize());
   if (handle_out) {
     cudaIpcMemHandle_t h;
@@ -1164,7 +1174,7 @@ extern "C" int b200moe_ep_dispatch(b200moe_ctx* ctx, int layer, const void* x_lo
   if (T_local > 0 && (rc = launch_router(ctx, layer, x_local, nullptr, T_local, ctx->ids64, ctx->scores, nullptr, st))) return rc;
   EpDispatchParams dp{};
   dp.x = x_local; dp.ids = ctx->ids64; dp.T_local = T_local; dp.E = c.num_experts; dp.g = ep.geom;
-  dp.epoch = ep.counters; dp.done = ep.counters + 1; dp.status = ctx->status;
+  dp.epoch = ep.counters; dp.done = ep.counters + 1; dp.dest_count = reinterpret_cast<int*>(ep.counters + 8); dp.status = ctx->status;
   const int pairs = T_local * c.top_k;
   const int grid = std::max(1, (pairs + kEpPairsPerCta - 1) / kEpPairsPerCta);
   ep.last_T_local = T_local;
@@ -1238,7 +1248,9 @@ extern "C" int b200moe_ep_experts(b200moe_ctx* ctx, int layer, int ffn_kind, voi
   EpReturnParams rp{};
   rp.y = ctx->y; rp.offsets = ctx->offsets; rp.sorted_pair = ctx->sorted_pair; rp.E = E; rp.g = g;
   rp.epoch = ep.counters; rp.done = ep.counters + 2; rp.status = ctx->status;
-  const int grid = std::max(1, std::min(rows, 4 * ctx->sm_count));
+  // rows actually received are about T_all*K/G; CTAs beyond them leave after one load
+  const int expect = (int)std::min<long long>(rows, 2LL * std::max(1, ep.last_T_local) * c.top_k + 64);
+  const int grid = std::max(1, std::min(expect, 8 * ctx->sm_count));
   return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
     using Tt = decltype(tag);
     ProfScope prof(ctx, B200MOE_KERNEL_EP_RETURN, st);

@@ -56,15 +56,18 @@ struct EpDispatchParams {
   EpGeom g;
   unsigned* epoch;        // this rank's call counter (device)
   unsigned* done;         // CTA arrival counter, zero between launches
+  int* dest_count;        // [kEpMaxRanks] rows sent to each rank in this call, zero between launches
   int* status;
 };
 
 // grid = ceil(pairs / kEpPairsPerCta) (at least 1).  Pair p = t*K+k goes to rank d = ids[p] / epr, row
 // "number of earlier pairs with the same destination" of region [d][me]: every source fills its region
-// densely and in pair order, so the layout does not depend on timing.
+// densely and in pair order, so the layout does not depend on timing.  Written for latency: every
+// dependent step is one round of loads that are all in flight together.
 template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_dispatch_kernel(EpDispatchParams p, EpPeers peers) {
+  static_assert(kEpPairsPerCta == 4, "the row copy below is unrolled for four pairs");
   __shared__ int s_cnt[kEpMaxRanks];
-  __shared__ int s_dst[kEpPairsPerCta], s_pos[kEpPairsPerCta], s_exp[kEpPairsPerCta];
+  __shared__ int s_dst[kEpPairsPerCta], s_pos[kEpPairsPerCta];
   __shared__ int s_last;
   const EpGeom& g = p.g;
   const int npairs = p.T_local * g.K;
@@ -73,46 +76,55 @@ template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_dispatch_
   pdl_wait();        // ids come from the router launched just before; the previous call's combine is complete too
   pdl_trigger();
   __syncthreads();
+  // this CTA's own pairs (lanes 0..3 of warp 0) and the destinations of all earlier pairs, in one round of loads
+  long long my_e = -1;
+  if (threadIdx.x < kEpPairsPerCta && p0 + (int)threadIdx.x < npairs) my_e = p.ids[p0 + threadIdx.x];
   for (int i = threadIdx.x; i < min(p0, npairs); i += kEpThreads) {
     const long long e = p.ids[i];
     if (e >= 0 && e < p.E) atomicAdd(&s_cnt[(int)e / g.epr], 1);
   }
   __syncthreads();
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < kEpPairsPerCta; ++i) {
-      const int pr = p0 + i;
-      s_dst[i] = -1;
-      if (pr < npairs) {
-        const long long e = p.ids[pr];
-        if (e >= 0 && e < p.E) {
-          const int d = (int)e / g.epr;
-          s_dst[i] = d; s_pos[i] = s_cnt[d]++; s_exp[i] = (int)e;
-        } else {
-          atomicOr(p.status, kDevBadExpertId);
-        }
+  if (threadIdx.x < 32) {
+    const bool mine = threadIdx.x < kEpPairsPerCta && p0 + (int)threadIdx.x < npairs;
+    const bool valid = mine && my_e >= 0 && my_e < p.E;
+    if (mine && !valid) atomicOr(p.status, kDevBadExpertId);
+    const int d = valid ? (int)my_e / g.epr : -1;
+    int before = 0;                               // earlier pairs of this CTA with the same destination
+#pragma unroll
+    for (int j = 0; j < kEpPairsPerCta; ++j) {
+      const int dj = __shfl_sync(0xffffffffu, d, j);
+      if (j < (int)threadIdx.x && dj == d) ++before;
+    }
+    if (threadIdx.x < kEpPairsPerCta) {
+      s_dst[threadIdx.x] = d;
+      s_pos[threadIdx.x] = valid ? s_cnt[d] + before : 0;
+      if (valid) {
+        atomicAdd(p.dest_count + d, 1);
+        const size_t row = (size_t)g.me * g.cap + s_pos[threadIdx.x];
+        if (s_pos[threadIdx.x] < g.cap) reinterpret_cast<int2*>(peers.base[d] + g.off_meta)[row] = make_int2((int)my_e, p0 + (int)threadIdx.x);
       }
     }
   }
   __syncthreads();
   const int nch = g.H / 8;
   constexpr int CB = 8 * (int)sizeof(T);
-  for (int i = 0; i < kEpPairsPerCta; ++i) {
-    const int d = s_dst[i];
-    if (d < 0 || s_pos[i] >= g.cap) continue;
-    const int pr = p0 + i;
-    const size_t row = (size_t)g.me * g.cap + s_pos[i];
-    unsigned char* dst = peers.base[d] + g.off_x + row * (size_t)g.H * sizeof(T);
-    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.x) + (size_t)(pr / g.K) * g.H * sizeof(T);
-    for (int c = threadIdx.x; c < nch; c += kEpThreads) {
-      if (sizeof(T) == 2) {
-        *reinterpret_cast<uint4*>(dst + (size_t)c * CB) = ldg_cached(src + (size_t)c * CB);
-      } else {
-        *reinterpret_cast<uint4*>(dst + (size_t)c * CB) = ldg_cached(src + (size_t)c * CB);
-        *reinterpret_cast<uint4*>(dst + (size_t)c * CB + 16) = ldg_cached(src + (size_t)c * CB + 16);
+  constexpr int V = (int)sizeof(T) == 2 ? 1 : 2;    // 16-byte pieces per chunk
+  const unsigned char* xb = reinterpret_cast<const unsigned char*>(p.x);
+  for (int c = threadIdx.x; c < nch * V; c += kEpThreads) {
+    uint4 v[kEpPairsPerCta];
+#pragma unroll
+    for (int i = 0; i < kEpPairsPerCta; ++i)      // the four rows' loads are in flight together
+      if (s_dst[i] >= 0) v[i] = ldg_cached(xb + (size_t)((p0 + i) / g.K) * g.H * sizeof(T) + (size_t)c * 16);
+#pragma unroll
+    for (int i = 0; i < kEpPairsPerCta; ++i) {
+      const int d = s_dst[i];
+      if (d >= 0 && s_pos[i] < g.cap) {
+        const size_t row = (size_t)g.me * g.cap + s_pos[i];
+        *reinterpret_cast<uint4*>(peers.base[d] + g.off_x + row * (size_t)g.H * sizeof(T) + (size_t)c * 16) = v[i];
       }
     }
-    if (threadIdx.x == 0) reinterpret_cast<int2*>(peers.base[d] + g.off_meta)[row] = make_int2(s_exp[i], pr);
   }
+  (void)CB;
   __threadfence_system();
   __syncthreads();
   if (threadIdx.x == 0) s_last = (atomicAdd(p.done, 1u) == gridDim.x - 1);
@@ -120,21 +132,15 @@ template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_dispatch_
   if (!s_last) return;
   // last CTA: every row of this rank has been written and fenced; publish counts, then the flags
   __threadfence_system();
-  if (threadIdx.x < kEpMaxRanks) s_cnt[threadIdx.x] = 0;
-  __syncthreads();
-  for (int i = threadIdx.x; i < npairs; i += kEpThreads) {
-    const long long e = p.ids[i];
-    if (e >= 0 && e < p.E) atomicAdd(&s_cnt[(int)e / g.epr], 1);
-  }
-  __syncthreads();
   const unsigned epoch = *p.epoch + 1u;
   if (threadIdx.x < g.G) {
     EpHeader* h = reinterpret_cast<EpHeader*>(peers.base[threadIdx.x]);
-    h->disp_count[g.me] = min(s_cnt[threadIdx.x], g.cap);
+    h->disp_count[g.me] = min(__ldcg(p.dest_count + threadIdx.x), g.cap);
     __threadfence_system();
     st_release_sys(&h->disp_flag[g.me], epoch);
   }
   __syncthreads();
+  if (threadIdx.x < kEpMaxRanks) p.dest_count[threadIdx.x] = 0;
   if (threadIdx.x == 0) { *p.epoch = epoch; *p.done = 0u; }
 }
 
@@ -150,29 +156,36 @@ struct EpReturnParams {
 };
 
 // One CTA per sorted row (grid-stride).  Rows of experts this rank does not serve are returned as zeros,
-// so that every pair row of every source is rewritten in every call.
+// so that every pair row of every source is rewritten in every call.  The row's data, its table entry and
+// the row count are fetched in one round; only the metadata lookup depends on the table entry.
 template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_return_kernel(EpReturnParams p, EpPeers peers, SlotTable st) {
   __shared__ int s_last;
   const EpGeom& g = p.g;
   pdl_wait();        // y comes from the down projection launched just before
   pdl_trigger();
-  const int total = min(p.offsets[p.E], g.G * g.cap);
   const int2* meta = reinterpret_cast<const int2*>(peers.base[g.me] + g.off_meta);
-  const int nch = g.H / 8;
-  constexpr int CB = 8 * (int)sizeof(T);
-  for (int pos = blockIdx.x; pos < total; pos += gridDim.x) {
-    const int row = p.sorted_pair[pos];
-    if (row < 0 || row >= g.G * g.cap) { if (threadIdx.x == 0) atomicOr(p.status, kDevBadOffsets); continue; }
+  const int nrows = g.G * g.cap;
+  constexpr int V = (int)sizeof(T) == 2 ? 1 : 2;
+  const int npiece = g.H / 8 * V;
+  const unsigned char* yb = reinterpret_cast<const unsigned char*>(p.y);
+  for (int pos = blockIdx.x; pos < nrows; pos += gridDim.x) {
+    const int total = min(__ldcg(p.offsets + p.E), nrows);
+    const int row = __ldcg(p.sorted_pair + pos);
+    uint4 v[2];
+    int np = 0;
+    for (int c = threadIdx.x; c < npiece && np < 2; c += kEpThreads) v[np++] = ld_cg16(yb + (size_t)pos * g.H * sizeof(T) + (size_t)c * 16);
+    if (pos >= total) break;                      // uniform: rows beyond the last sent one (the loads above stayed inside the workspace)
+    if (row < 0 || row >= nrows) { if (threadIdx.x == 0) atomicOr(p.status, kDevBadOffsets); continue; }
     const int s = row / g.cap;
     const int2 m = __ldcg(meta + row);
     if (m.y < 0 || m.y >= g.cap) { if (threadIdx.x == 0) atomicOr(p.status, kDevBadOffsets); continue; }
     const bool served = m.x >= 0 && m.x < p.E && st.slot[m.x] >= 0;
     unsigned char* dst = peers.base[s] + g.off_ret + (size_t)m.y * g.H * sizeof(T);
-    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.y) + (size_t)pos * g.H * sizeof(T);
-    for (int c = threadIdx.x; c < nch; c += kEpThreads) {
-      const uint4 z = make_uint4(0, 0, 0, 0);
-      *reinterpret_cast<uint4*>(dst + (size_t)c * CB) = served ? ld_cg16(src + (size_t)c * CB) : z;
-      if (sizeof(T) == 4) *reinterpret_cast<uint4*>(dst + (size_t)c * CB + 16) = served ? ld_cg16(src + (size_t)c * CB + 16) : z;
+    const uint4 z = make_uint4(0, 0, 0, 0);
+    int ip = 0;
+    for (int c = threadIdx.x; c < npiece; c += kEpThreads, ++ip) {
+      const uint4 val = ip < 2 ? v[ip] : ld_cg16(yb + (size_t)pos * g.H * sizeof(T) + (size_t)c * 16);
+      *reinterpret_cast<uint4*>(dst + (size_t)c * 16) = served ? val : z;
     }
   }
   __threadfence_system();
