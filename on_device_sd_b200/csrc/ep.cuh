@@ -75,6 +75,7 @@ template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_dispatch_
   if (threadIdx.x < kEpMaxRanks) s_cnt[threadIdx.x] = 0;
   pdl_wait();        // ids come from the router launched just before; the previous call's combine is complete too
   pdl_trigger();
+  const unsigned epoch = *p.epoch + 1u;      // read early: only the last CTA uses it, and nobody writes it before every CTA has arrived
   __syncthreads();
   // this CTA's own pairs (lanes 0..3 of warp 0) and the destinations of all earlier pairs, in one round of loads
   long long my_e = -1;
@@ -130,13 +131,12 @@ template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_dispatch_
   if (threadIdx.x == 0) s_last = (atomicAdd(p.done, 1u) == gridDim.x - 1);
   __syncthreads();
   if (!s_last) return;
-  // last CTA: every row of this rank has been written and fenced; publish counts, then the flags
-  __threadfence_system();
-  const unsigned epoch = *p.epoch + 1u;
+  // Last CTA: every CTA fenced its rows at system scope before it arrived on `done`, and this CTA has observed
+  // all arrivals; the release store below (a system-scope fence followed by the store) therefore orders all of
+  // them, and the count written just before it by the same thread, ahead of the flag.
   if (threadIdx.x < g.G) {
     EpHeader* h = reinterpret_cast<EpHeader*>(peers.base[threadIdx.x]);
     h->disp_count[g.me] = min(__ldcg(p.dest_count + threadIdx.x), g.cap);
-    __threadfence_system();
     st_release_sys(&h->disp_flag[g.me], epoch);
   }
   __syncthreads();
@@ -163,6 +163,7 @@ template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_return_ke
   const EpGeom& g = p.g;
   pdl_wait();        // y comes from the down projection launched just before
   pdl_trigger();
+  const unsigned epoch = *p.epoch;
   const int2* meta = reinterpret_cast<const int2*>(peers.base[g.me] + g.off_meta);
   const int nrows = g.G * g.cap;
   constexpr int V = (int)sizeof(T) == 2 ? 1 : 2;
@@ -193,9 +194,7 @@ template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_return_ke
   if (threadIdx.x == 0) s_last = (atomicAdd(p.done, 1u) == gridDim.x - 1);
   __syncthreads();
   if (!s_last) return;
-  __threadfence_system();
-  const unsigned epoch = *p.epoch;
-  if (threadIdx.x < g.G) st_release_sys(&reinterpret_cast<EpHeader*>(peers.base[threadIdx.x])->ret_flag[g.me], epoch);
+  if (threadIdx.x < g.G) st_release_sys(&reinterpret_cast<EpHeader*>(peers.base[threadIdx.x])->ret_flag[g.me], epoch);   // see ep_dispatch_kernel
   if (threadIdx.x == 0) *p.done = 0u;
 }
 
