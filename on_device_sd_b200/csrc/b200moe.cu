@@ -472,7 +472,7 @@ struct RouterNorm {          // RMSNorm fused into the router's load of the toke
 
 static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void* logits, int T, int64_t* ids_out,
                          void* scores_out, unsigned long long* bitmap_dev, cudaStream_t st, const PermuteParams* fuse = nullptr,
-                         const SlotTable* tab = nullptr, const RouterNorm* norm = nullptr) {
+                         const SlotTable* tab = nullptr, const RouterNorm* norm = nullptr, bool ep_dispatch = false) {
   const b200moe_config& c = ctx->cfg;
   RouterParams p{};
   p.x = x;
@@ -494,6 +494,12 @@ static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void*
     if (c.hidden_size % 8 || c.hidden_size > kNormThreads * kNormMaxChunks * 8)
       return fail(ctx, B200MOE_E_UNSUPPORTED, "fused norm: hidden size %d (multiples of 8 up to %d)", c.hidden_size, kNormThreads * kNormMaxChunks * 8);
   }
+  EpPeers peers{};
+  if (ep_dispatch) {       // the routed rows leave for their owners from the router's own tail
+    p.ep_dispatch = 1; p.epg = ctx->ep.geom; p.ep_epoch = ctx->ep.counters; p.ep_dest_count = reinterpret_cast<int*>(ctx->ep.counters + 8);
+    p.ep_status = ctx->status;
+    peers = ctx->ep.peers;
+  }
   SlotTable none;
   if (fuse && tab) { p.fuse_permute = 1; p.perm = *fuse; }
   else { identity_slots(none); tab = &none; }
@@ -514,9 +520,9 @@ static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void*
           CUDA_TRY(ctx, cudaFuncSetAttribute(kn, cudaFuncAttributeMaxDynamicSharedMemorySize, 64 * 1024));
           configured_n.done(c.device);
         }
-        launch_chain(kn, dim3(T, ey), dim3(kRouterThreads), row, st, p, *tab);
+        launch_chain(kn, dim3(T, ey), dim3(kRouterThreads), row, st, p, *tab, peers);
       } else {
-        launch_chain(router_kernel<Tt, 1, 8>, dim3(T, ey), dim3(kRouterThreads), 0, st, p, *tab);
+        launch_chain(router_kernel<Tt, 1, 8>, dim3(T, ey), dim3(kRouterThreads), 0, st, p, *tab, peers);
       }
       return post_launch(ctx, "router_kernel");
     }
@@ -535,7 +541,7 @@ static int launch_router(b200moe_ctx* ctx, int layer, const void* x, const void*
     }
     if (smem > 160 * 1024) return fail(ctx, B200MOE_E_UNSUPPORTED, "router: hidden size %d too large for the token tile", c.hidden_size);
     const dim3 grid((T + kTileTokens - 1) / kTileTokens, (c.num_experts + 7) / 8);
-    launch_chain(with_norm ? k1n : k1, grid, dim3(kRouterThreads), smem, st, p, *tab);
+    launch_chain(with_norm ? k1n : k1, grid, dim3(kRouterThreads), smem, st, p, *tab, peers);
     return post_launch(ctx, "router_tile_kernel");
   });
 }
@@ -1171,17 +1177,17 @@ extern "C" int b200moe_ep_dispatch(b200moe_ctx* ctx, int layer, const void* x_lo
   if (!ctx->gate_w[layer]) return fail(ctx, B200MOE_E_STATE, "b200moe_ep_dispatch: no gate weight registered for layer %d", layer);
   CUDA_TRY(ctx, cudaSetDevice(c.device));
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (T_local > 0 && (rc = launch_router(ctx, layer, x_local, nullptr, T_local, ctx->ids64, ctx->scores, nullptr, st))) return rc;
-  EpDispatchParams dp{};
-  dp.x = x_local; dp.ids = ctx->ids64; dp.T_local = T_local; dp.E = c.num_experts; dp.g = ep.geom;
-  dp.epoch = ep.counters; dp.done = ep.counters + 1; dp.dest_count = reinterpret_cast<int*>(ep.counters + 8); dp.status = ctx->status;
-  const int pairs = T_local * c.top_k;
-  const int grid = std::max(1, (pairs + kEpPairsPerCta - 1) / kEpPairsPerCta);
   ep.last_T_local = T_local;
+  if (T_local > 0)       // router + dispatch in one launch: each routed tile's rows leave from the router's tail
+    return launch_router(ctx, layer, x_local, nullptr, T_local, ctx->ids64, ctx->scores, nullptr, st, nullptr, nullptr, nullptr, true);
+  // no tokens on this rank: it still has to tell every peer so
+  EpDispatchParams dp{};
+  dp.x = x_local; dp.ids = ctx->ids64; dp.T_local = 0; dp.E = c.num_experts; dp.g = ep.geom;
+  dp.epoch = ep.counters; dp.done = ep.counters + 1; dp.dest_count = reinterpret_cast<int*>(ep.counters + 8); dp.status = ctx->status;
   return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
     using Tt = decltype(tag);
     ProfScope prof(ctx, B200MOE_KERNEL_EP_DISPATCH, st);
-    launch_chain(ep_dispatch_kernel<Tt>, dim3(grid), dim3(kEpThreads), 0, st, dp, ep.peers);
+    launch_chain(ep_dispatch_kernel<Tt>, dim3(1), dim3(kEpThreads), 0, st, dp, ep.peers);
     return post_launch(ctx, "ep_dispatch_kernel");
   });
 }
@@ -1211,7 +1217,10 @@ extern "C" int b200moe_ep_experts(b200moe_ctx* ctx, int layer, int ffn_kind, voi
   pp.ep_meta = reinterpret_cast<const int2*>(ep.base + g.off_meta);
   pp.ep_count = hdr->disp_count; pp.ep_flags = hdr->disp_flag; pp.ep_epoch = ep.counters;
   pp.ep_G = g.G; pp.ep_cap = g.cap; pp.ep_wait_cycles = ep.wait_cycles;
-  const int pthreads = std::min(kPermuteMaxThreads, std::max(256, (rows + 31) / 32 * 32));
+  // the CTA is sized for the rows this rank can expect (about T_local*K when the routing is balanced), not for
+  // the capacity of its receive buffer: fewer warps mean shorter scans; any number of rows is still handled
+  const int expect_rows = (int)std::min<long long>(rows, 2LL * std::max(1, ep.last_T_local) * c.top_k + 64);
+  const int pthreads = std::min(kPermuteMaxThreads, std::max(256, (expect_rows + 31) / 32 * 32));
   const size_t smem = (size_t)((pthreads / 32) * E + E) * sizeof(int);
   {
     ProfScope prof(ctx, B200MOE_KERNEL_PERMUTE, st);

@@ -15,6 +15,7 @@
 #pragma once
 #include <type_traits>
 #include "common.cuh"
+#include "ep.cuh"
 #include "permute.cuh"
 #include "rmsnorm.cuh"
 
@@ -49,9 +50,76 @@ struct RouterParams {
   void* normed_out;
   void* res_out;
   float norm_eps;
+  // Expert-parallel dispatch fused into the tail (ep_dispatch set): the CTA that has just routed a token tile
+  // stores each of its tokens' rows into the receive region of the rank that owns the chosen expert, the CTA
+  // that finishes the last tile publishes the row counts and raises the flags (the work of ep_dispatch_kernel,
+  // without its launch and without its second pass over the ids).  Row positions inside a region are handed
+  // out by an atomic counter per destination, so their order varies from run to run; results do not, every
+  // row is computed on its own and carries its pair index.
+  int ep_dispatch;
+  EpGeom epg;
+  unsigned* ep_epoch;
+  int* ep_dest_count;
+  int* ep_status;
 };
 
 constexpr int kRouterFuseSmemInts = (kRouterThreads / 32 + 1) * kMaxExperts;
+
+// Expert-parallel tail: called by every thread of a CTA that has just finished the top-k of the tokens
+// t0 .. t0+ntok-1.  Pairs are dealt to the CTA's warps; a warp copies one token row (16-byte pieces, eight in
+// flight per lane) into the owner's receive region.
+template <typename T>
+__device__ __forceinline__ void router_dispatch_tail(const RouterParams& p, const EpPeers& peers, int t0, int ntok, unsigned n_tiles) {
+  __shared__ int s_alld;
+  const EpGeom& g = p.epg;
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  __syncthreads();                       // the ids of this tile's tokens have been written by this CTA's warps
+  const unsigned epoch = *p.ep_epoch + 1u;
+  const int npairs = ntok * g.K;
+  const int npiece = g.H / 8 * ((int)sizeof(T) == 2 ? 1 : 2);
+  for (int pi = warp; pi < npairs; pi += kRouterThreads / 32) {
+    const int t = t0 + pi / g.K;
+    const int pr = t * g.K + pi % g.K;
+    const long long e = __ldcg(reinterpret_cast<const long long*>(p.ids64) + pr);
+    if (e < 0 || e >= p.E) continue;
+    const int d = (int)e / g.epr;
+    int pos = 0;
+    if (lane == 0) pos = atomicAdd(p.ep_dest_count + d, 1);
+    pos = __shfl_sync(0xffffffffu, pos, 0);
+    if (pos >= g.cap) { if (lane == 0) atomicOr(p.ep_status, kDevBadOffsets); continue; }
+    const size_t row = (size_t)g.me * g.cap + pos;
+    const unsigned char* src = reinterpret_cast<const unsigned char*>(p.x) + (size_t)t * g.H * sizeof(T);
+    unsigned char* dst = peers.base[d] + g.off_x + row * (size_t)g.H * sizeof(T);
+    for (int c0 = lane; c0 < npiece; c0 += 32 * 8) {
+      uint4 v[8];
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (c0 + 32 * u < npiece) v[u] = ldg_cached(src + (size_t)(c0 + 32 * u) * 16);
+#pragma unroll
+      for (int u = 0; u < 8; ++u)
+        if (c0 + 32 * u < npiece) *reinterpret_cast<uint4*>(dst + (size_t)(c0 + 32 * u) * 16) = v[u];
+    }
+    if (lane == 0) reinterpret_cast<int2*>(peers.base[d] + g.off_meta)[row] = make_int2((int)e, pr);
+  }
+  __threadfence_system();
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    const unsigned prev = atomicAdd(p.all_done, 1u);
+    s_alld = (prev == n_tiles - 1);
+    if (s_alld) *p.all_done = 0u;
+  }
+  __syncthreads();
+  if (!s_alld) return;
+  // every tile's CTA fenced its rows before it arrived; the release store orders them, and the count, ahead of the flag
+  if (threadIdx.x < g.G) {
+    EpHeader* h = reinterpret_cast<EpHeader*>(peers.base[threadIdx.x]);
+    h->disp_count[g.me] = min(__ldcg(p.ep_dest_count + threadIdx.x), g.cap);
+    st_release_sys(&h->disp_flag[g.me], epoch);
+  }
+  __syncthreads();
+  if (threadIdx.x < kEpMaxRanks) p.ep_dest_count[threadIdx.x] = 0;
+  if (threadIdx.x == 0) *p.ep_epoch = epoch;
+}
 
 // Tail shared by the router kernels: called by every thread of a CTA that has just finished the top-k of a
 // token tile.  Returns after the grouping when this CTA was the last one of the grid.
@@ -215,7 +283,7 @@ __device__ void topk_softmax_token(const RouterParams& p, int t, int lane, float
 // The CTA that finishes a tile last runs phase 2 (top-k) for its tokens; the counter returns to
 // zero for the next call.  TT = 1 with 8 chunk positions per trip serves small batches
 // (latency-bound: every load of a row is in flight at once); TT = 4 amortises the weight row.
-template <typename T, int TT, int U, bool NORM = false> __global__ void __launch_bounds__(kRouterThreads) router_kernel(RouterParams p, SlotTable st) {
+template <typename T, int TT, int U, bool NORM = false> __global__ void __launch_bounds__(kRouterThreads) router_kernel(RouterParams p, SlotTable st, EpPeers peers) {
   static_assert(!NORM || TT == 1, "the fused norm stages one token row per CTA");
   static_assert(kNormThreads == kRouterThreads, "rmsnorm_row is written for the router's CTA size");
   extern __shared__ __align__(16) unsigned char xrow_raw[];       // NORM: the normalised row of this CTA's token
@@ -319,6 +387,7 @@ template <typename T, int TT, int U, bool NORM = false> __global__ void __launch
   __threadfence();
   if (warp < TT && t0 + warp < p.T) topk_softmax_token<T>(p, t0 + warp, lane, skey[warp], sidx[warp]);
   if (p.fuse_permute) router_fused_tail(p, st, gridDim.x, s_perm);
+  if (p.ep_dispatch) router_dispatch_tail<T>(p, peers, t0, min(TT, p.T - t0), gridDim.x);
 }
 
 // Larger batches (T > 16): a CTA owns a tile of TT tokens x (8 * EPW) experts.  The token tile is staged
@@ -328,7 +397,7 @@ template <typename T, int TT, int U, bool NORM = false> __global__ void __launch
 // roundings, then 1 + 5 for the pair and the warp tree.  Small tiles (4 tokens x 8 experts) keep a CTA's
 // serial chain short - a warp reduces TT * EPW sums one after the other - and give the grid enough CTAs.
 constexpr int kTileTokens = 4;
-template <typename T, int TT, int EPW, bool NORM = false> __global__ void __launch_bounds__(kRouterThreads) router_tile_kernel(RouterParams p, SlotTable st) {
+template <typename T, int TT, int EPW, bool NORM = false> __global__ void __launch_bounds__(kRouterThreads) router_tile_kernel(RouterParams p, SlotTable st, EpPeers peers) {
   __shared__ float s_part[kNormThreads / 32];
   __shared__ float s_scale;
   constexpr bool kExact = std::is_same<T, float>::value;
@@ -458,6 +527,7 @@ template <typename T, int TT, int EPW, bool NORM = false> __global__ void __laun
   __threadfence();
   if (warp < TT && t0 + warp < p.T) topk_softmax_token<T>(p, t0 + warp, lane, skey[warp], sidx[warp]);
   if (p.fuse_permute) router_fused_tail(p, st, gridDim.x, s_perm);
+  if (p.ep_dispatch) router_dispatch_tail<T>(p, peers, t0, min(TT, p.T - t0), gridDim.x);
 }
 
 // Top-k / softmax on caller-supplied logits: one warp per token.
