@@ -1259,7 +1259,7 @@ extern "C" int b200moe_ep_experts(b200moe_ctx* ctx, int layer, int ffn_kind, voi
   rp.epoch = ep.counters; rp.done = ep.counters + 2; rp.status = ctx->status;
   // rows actually received are about T_all*K/G; CTAs beyond them leave after one load
   const int expect = (int)std::min<long long>(rows, 2LL * std::max(1, ep.last_T_local) * c.top_k + 64);
-  const int grid = std::max(1, std::min(expect, 8 * ctx->sm_count));
+  const int grid = std::max(1, std::min((expect + kEpRowsPerTrip - 1) / kEpRowsPerTrip, 4 * ctx->sm_count));
   return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) {
     using Tt = decltype(tag);
     ProfScope prof(ctx, B200MOE_KERNEL_EP_RETURN, st);

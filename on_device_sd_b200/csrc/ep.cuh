@@ -155,39 +155,56 @@ struct EpReturnParams {
   int* status;
 };
 
-// One CTA per sorted row (grid-stride).  Rows of experts this rank does not serve are returned as zeros,
-// so that every pair row of every source is rewritten in every call.  The row's data, its table entry and
-// the row count are fetched in one round; only the metadata lookup depends on the table entry.
+constexpr int kEpRowsPerTrip = 4;
+
+// A CTA returns kEpRowsPerTrip sorted rows per trip (grid-stride).  Rows of experts this rank does not serve are
+// returned as zeros, so that every pair row of every source is rewritten in every call.  One thread per row
+// resolves the table entry and the metadata; the copy then keeps the rows' loads in flight together; the
+// system-scope fence is paid once per CTA, not once per row.
 template <typename T> __global__ void __launch_bounds__(kEpThreads) ep_return_kernel(EpReturnParams p, EpPeers peers, SlotTable st) {
+  static_assert(kEpRowsPerTrip == 4, "the copy below is unrolled for four rows");
   __shared__ int s_last;
+  __shared__ int s_src[kEpRowsPerTrip], s_pair[kEpRowsPerTrip], s_served[kEpRowsPerTrip];
   const EpGeom& g = p.g;
   pdl_wait();        // y comes from the down projection launched just before
   pdl_trigger();
   const unsigned epoch = *p.epoch;
   const int2* meta = reinterpret_cast<const int2*>(peers.base[g.me] + g.off_meta);
   const int nrows = g.G * g.cap;
-  constexpr int V = (int)sizeof(T) == 2 ? 1 : 2;
-  const int npiece = g.H / 8 * V;
+  const int total = min(__ldcg(p.offsets + p.E), nrows);
+  const int npiece = g.H / 8 * ((int)sizeof(T) == 2 ? 1 : 2);
+  const size_t row_bytes = (size_t)g.H * sizeof(T);
   const unsigned char* yb = reinterpret_cast<const unsigned char*>(p.y);
-  for (int pos = blockIdx.x; pos < nrows; pos += gridDim.x) {
-    const int total = min(__ldcg(p.offsets + p.E), nrows);
-    const int row = __ldcg(p.sorted_pair + pos);
-    uint4 v[2];
-    int np = 0;
-    for (int c = threadIdx.x; c < npiece && np < 2; c += kEpThreads) v[np++] = ld_cg16(yb + (size_t)pos * g.H * sizeof(T) + (size_t)c * 16);
-    if (pos >= total) break;                      // uniform: rows beyond the last sent one (the loads above stayed inside the workspace)
-    if (row < 0 || row >= nrows) { if (threadIdx.x == 0) atomicOr(p.status, kDevBadOffsets); continue; }
-    const int s = row / g.cap;
-    const int2 m = __ldcg(meta + row);
-    if (m.y < 0 || m.y >= g.cap) { if (threadIdx.x == 0) atomicOr(p.status, kDevBadOffsets); continue; }
-    const bool served = m.x >= 0 && m.x < p.E && st.slot[m.x] >= 0;
-    unsigned char* dst = peers.base[s] + g.off_ret + (size_t)m.y * g.H * sizeof(T);
-    const uint4 z = make_uint4(0, 0, 0, 0);
-    int ip = 0;
-    for (int c = threadIdx.x; c < npiece; c += kEpThreads, ++ip) {
-      const uint4 val = ip < 2 ? v[ip] : ld_cg16(yb + (size_t)pos * g.H * sizeof(T) + (size_t)c * 16);
-      *reinterpret_cast<uint4*>(dst + (size_t)c * 16) = served ? val : z;
+  for (int base = blockIdx.x * kEpRowsPerTrip; base < total; base += gridDim.x * kEpRowsPerTrip) {
+    if (threadIdx.x < kEpRowsPerTrip) {
+      int src = -1, pair = 0, served = 0;
+      const int pos = base + threadIdx.x;
+      if (pos < total) {
+        const int row = __ldcg(p.sorted_pair + pos);
+        if (row >= 0 && row < nrows) {
+          const int2 m = __ldcg(meta + row);
+          if (m.y >= 0 && m.y < g.cap) {
+            src = row / g.cap; pair = m.y;
+            served = (m.x >= 0 && m.x < p.E && st.slot[m.x] >= 0) ? 1 : 0;
+          }
+        }
+        if (src < 0) atomicOr(p.status, kDevBadOffsets);
+      }
+      s_src[threadIdx.x] = src; s_pair[threadIdx.x] = pair; s_served[threadIdx.x] = served;
     }
+    __syncthreads();
+    for (int c = threadIdx.x; c < npiece; c += kEpThreads) {
+      uint4 v[kEpRowsPerTrip];
+#pragma unroll
+      for (int i = 0; i < kEpRowsPerTrip; ++i) {
+        v[i] = make_uint4(0, 0, 0, 0);
+        if (s_src[i] >= 0 && s_served[i]) v[i] = ld_cg16(yb + (size_t)(base + i) * row_bytes + (size_t)c * 16);
+      }
+#pragma unroll
+      for (int i = 0; i < kEpRowsPerTrip; ++i)
+        if (s_src[i] >= 0) *reinterpret_cast<uint4*>(peers.base[s_src[i]] + g.off_ret + (size_t)s_pair[i] * row_bytes + (size_t)c * 16) = v[i];
+    }
+    __syncthreads();
   }
   __threadfence_system();
   __syncthreads();
