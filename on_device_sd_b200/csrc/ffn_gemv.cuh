@@ -363,12 +363,22 @@ template <typename T> __global__ void __launch_bounds__(kCombineThreads) combine
             // the down projection's value is the sum of its K slices, added in slice order and
             // rounded to the model dtype once - the rounding point of the reference's F.linear
             const float* src = p.ypart + (size_t)s_pos[s_order[j0 + u]] * p.H + c * 8;
-            float4 a = __ldg(reinterpret_cast<const float4*>(src)), b = __ldg(reinterpret_cast<const float4*>(src) + 1);
-            yf[0] = a.x; yf[1] = a.y; yf[2] = a.z; yf[3] = a.w; yf[4] = b.x; yf[5] = b.y; yf[6] = b.z; yf[7] = b.w;
-            for (int sl = 1; sl < p.y_parts; ++sl) {
-              const float* q = src + (size_t)sl * p.pairs_cap * p.H;
-              a = __ldg(reinterpret_cast<const float4*>(q)); b = __ldg(reinterpret_cast<const float4*>(q) + 1);
-              yf[0] += a.x; yf[1] += a.y; yf[2] += a.z; yf[3] += a.w; yf[4] += b.x; yf[5] += b.y; yf[6] += b.z; yf[7] += b.w;
+#pragma unroll
+            for (int i = 0; i < 8; ++i) yf[i] = 0.0f;
+            for (int sl0 = 0; sl0 < p.y_parts; sl0 += 4) {        // four slices' loads in flight, added in slice order
+              float4 a[4], b[4];
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                if (sl0 + q < p.y_parts) {
+                  const float* qp = src + (size_t)(sl0 + q) * p.pairs_cap * p.H;
+                  a[q] = __ldg(reinterpret_cast<const float4*>(qp)); b[q] = __ldg(reinterpret_cast<const float4*>(qp) + 1);
+                }
+#pragma unroll
+              for (int q = 0; q < 4; ++q)
+                if (sl0 + q < p.y_parts) {
+                  if (sl0 + q == 0) { yf[0] = a[q].x; yf[1] = a[q].y; yf[2] = a[q].z; yf[3] = a[q].w; yf[4] = b[q].x; yf[5] = b[q].y; yf[6] = b[q].z; yf[7] = b[q].w; }
+                  else { yf[0] += a[q].x; yf[1] += a[q].y; yf[2] += a[q].z; yf[3] += a[q].w; yf[4] += b[q].x; yf[5] += b[q].y; yf[6] += b[q].z; yf[7] += b[q].w; }
+                }
             }
 #pragma unroll
             for (int i = 0; i < 8; ++i) yf[i] = rn<T>(yf[i]);
