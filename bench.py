@@ -362,7 +362,9 @@ def per_batch_table(w: Workload, peak: float):
 
 def roofline_record(w: Workload, prof, ms_per_step, peak, peak_kind):
     """Roofline of the dominant kernel (gate/up weight streaming): bytes per launch / mean launch time."""
-    gu_bytes = sum(algorithmic_bytes(w.H, w.E, w.I, T, w.n_active[T], w.int4)[1] for T in w.batches) / len(w.batches)
+    # a single-token batch that ran as the one-launch block has no gate/up launch of its own
+    gu_batches = [T for T in w.batches if not (T == 1 and prof.get("token_block", (0.0, 0))[1])] or list(w.batches)
+    gu_bytes = sum(algorithmic_bytes(w.H, w.E, w.I, T, w.n_active[T], w.int4)[1] for T in gu_batches) / len(gu_batches)
     layer_bytes = sum(algorithmic_bytes(w.H, w.E, w.I, T, w.n_active[T], w.int4)[0] for T in w.batches)
     gu_ms, gu_n = prof["ffn_gate_up"]
     achieved = gu_bytes / (gu_ms / max(gu_n, 1) * 1e-3) / 1e9 if gu_ms > 0 else None

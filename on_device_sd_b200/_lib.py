@@ -20,7 +20,7 @@ FFN_AUTO, FFN_GEMV, FFN_MMA = 0, 1, 2
 MAX_EXPERTS, MAX_TOPK = 256, 32
 EP_HANDLE_BYTES = 64
 KERNEL_CLASSES = 8
-KERNEL_NAMES = ("router", "permute", "ffn_gate_up", "ffn_down", "combine", "ep_dispatch", "ep_return")
+KERNEL_NAMES = ("router", "permute", "ffn_gate_up", "ffn_down", "combine", "ep_dispatch", "ep_return", "token_block")
 ABI_VERSION = 2
 
 
@@ -69,6 +69,7 @@ PROTOTYPES = {
     "b200moe_unpack_int4": (c_int, [c_void_p, c_void_p, c_int, c_int, c_int, c_void_p, c_void_p, c_void_p]),
     "b200moe_profile": (c_int, [c_void_p, c_int]),
     "b200moe_profile_read": (c_int, [c_void_p, c_void_p, c_void_p]),
+    "b200moe_set_token_kernel": (c_int, [c_void_p, c_int]),
     "b200moe_status": (c_int, [c_void_p, POINTER(c_int), c_void_p]),
     "b200moe_launch_count": (c_int64, [c_void_p]),
 }

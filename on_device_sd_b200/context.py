@@ -344,6 +344,10 @@ class MoEContext:
         self._check(self._lib.b200moe_profile_read(self._h, ms, n))
         return {name: (float(ms[i]), int(n[i])) for i, name in enumerate(_lib.KERNEL_NAMES)}
 
+    def set_token_kernel(self, enable: bool) -> None:
+        """Single-token batches of `forward_fused` run as one cooperative launch (default) or through the kernel chain."""
+        self._check(self._lib.b200moe_set_token_kernel(self._h, 1 if enable else 0))
+
     def status(self) -> int:
         """Synchronises the current stream and returns the device status word (0 = clean); raises when it is not."""
         v = c_int(0)

@@ -31,6 +31,7 @@
 #ifdef B200MOE_WITH_UMMA
 #include "ffn_umma.cuh"
 #endif
+#include "moe_token.cuh"
 
 using namespace b200moe;
 
@@ -56,7 +57,7 @@ struct b200moe_ctx {
 #endif
   // workspace
   float* logits = nullptr;          // [Tm,E] rounded logits of the latest router launch, as fp32
-  unsigned* tile_counter = nullptr;
+  unsigned* tile_counter = nullptr;     // [Tm] one per token tile, [Tm] all tiles done, [Tm+1] grid barrier word of the single-token kernel
   int64_t* ids64 = nullptr;
   void* scores = nullptr;
   int* offsets = nullptr;
@@ -72,6 +73,7 @@ struct b200moe_ctx {
   float* ypart = nullptr;           // fp32 K-slices of the down projection (tensor-core path)
   int ypart_slices = 0;             // slices ypart has room for
   int last_ksplit = 1;              // K split used by the most recent tensor-core launch
+  bool token_kernel = true;         // single-token batches of the fused entry take the one-launch kernel (b200moe_set_token_kernel)
   int* status = nullptr;
   unsigned long long* bitmap = nullptr;
   // second, tiny table set used by b200moe_expert_ffn (one expert, identity permutation)
@@ -221,7 +223,7 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
   char* sb = nullptr;
   const size_t pairs = Tm * K;
   if ((rc = dev_alloc(ctx, &ctx->d_experts, L * E + 1)) || (rc = dev_alloc(ctx, &ctx->logits, Tm * E)) ||
-      (rc = dev_alloc(ctx, &ctx->tile_counter, Tm + 1)) || (rc = dev_alloc(ctx, &ctx->ids64, pairs)) ||
+      (rc = dev_alloc(ctx, &ctx->tile_counter, Tm + 2)) || (rc = dev_alloc(ctx, &ctx->ids64, pairs)) ||
       (rc = dev_alloc(ctx, &sb, pairs * 4)) || (rc = dev_alloc(ctx, &ctx->offsets, (size_t)E + 1)) ||
       (rc = dev_alloc(ctx, &ctx->sorted_pair, pairs)) || (rc = dev_alloc(ctx, &ctx->inv, pairs)) ||
       (rc = dev_alloc(ctx, &ctx->act_list, (size_t)E)) || (rc = dev_alloc(ctx, &ctx->n_act, 4)) ||
@@ -282,7 +284,7 @@ extern "C" int b200moe_create(const b200moe_config* cfg, b200moe_ctx** out) {
       ctx->encode_fn = nullptr;   // the tensor-core path then reports itself unsupported
   }
 #endif
-  cudaMemset(ctx->tile_counter, 0, (Tm + 1) * sizeof(unsigned));
+  cudaMemset(ctx->tile_counter, 0, (Tm + 2) * sizeof(unsigned));
   cudaMemset(ctx->status, 0, sizeof(int));
   cudaMemset(ctx->d_experts, 0, (L * E + 1) * sizeof(ExpertPtrs));
   {
@@ -905,6 +907,66 @@ static int launch_ffn(b200moe_ctx* ctx, const FfnLaunch& f, const SlotTable& st,
   });
 }
 
+// Single-token batch of a dense 16-bit model through the fused entry: one cooperative launch (moe_token.cuh).
+// Returns B200MOE_E_UNSUPPORTED (without recording an error) when the shape or the device cannot take it.
+static int launch_token(b200moe_ctx* ctx, int layer, const void* x, int64_t* ids, void* scores, const void* residual, void* out,
+                        const PermuteParams& pp, const SlotTable& tab, const RouterNorm* norm, cudaStream_t st) {
+  const b200moe_config& c = ctx->cfg;
+  if (c.weight_mode != B200MOE_W_DENSE || c.act_dtype == B200MOE_F32) return B200MOE_E_UNSUPPORTED;
+  if (c.hidden_size % 8 || c.intermediate_size % 8 || (size_t)c.hidden_size * 2 > (size_t)kTokenMaxRowBytes) return B200MOE_E_UNSUPPORTED;
+  using S = GemvDefault;
+  TokenParams p{};
+  p.r.x = x; p.r.wg = ctx->gate_w[layer]; p.r.bias = ctx->gate_bias[layer];
+  p.r.logits = ctx->logits; p.r.ids64 = ids; p.r.scores = scores;
+  p.r.T = 1; p.r.H = c.hidden_size; p.r.E = c.num_experts; p.r.K = c.top_k;
+  p.r.perm = pp;
+  if (norm && norm->weight) {
+    if (c.hidden_size > kNormMaxChunks * kNormThreads * 8) return B200MOE_E_UNSUPPORTED;
+    p.r.norm_res = norm->residual; p.r.norm_w = norm->weight; p.r.norm_eps = norm->eps;
+    p.r.normed_out = norm->normed_out; p.r.res_out = norm->res_out;
+  }
+  p.experts = ctx->d_experts + (size_t)layer * c.num_experts;
+  p.h = ctx->h; p.y = ctx->y; p.residual = residual; p.out = out; p.I = c.intermediate_size;
+  p.gbar = ctx->tile_counter + c.max_tokens + 1;
+  p.status = ctx->status;
+  p.wait_cycles = 1ll << 31;
+  return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) -> int {
+    using Tt = decltype(tag);
+    if constexpr (sizeof(Tt) != 2) {
+      return B200MOE_E_UNSUPPORTED;
+    } else {
+      auto kn = moe_token_kernel<Tt, S>;
+      constexpr size_t smem = token_smem_bytes<S>();
+      static ConfiguredDevices configured, usable;   // per template instance
+      if (configured.needs(c.device)) {
+        int coop = 0, per_sm = 0;
+        cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c.device);
+        if (cudaFuncSetAttribute(kn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem) == cudaSuccess &&
+            cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kn, S::THREADS, smem) == cudaSuccess && coop && per_sm >= 1)
+          usable.done(c.device);
+        cudaGetLastError();
+        configured.done(c.device);
+      }
+      if (usable.needs(c.device)) return B200MOE_E_UNSUPPORTED;
+      cudaLaunchConfig_t cfg = {};
+      cfg.gridDim = dim3(ctx->sm_count);
+      cfg.blockDim = dim3(S::THREADS);
+      cfg.dynamicSmemBytes = smem;
+      cfg.stream = st;
+      cudaLaunchAttribute attr[1];
+      attr[0].id = cudaLaunchAttributeCooperative;     // every CTA resident: the grid barriers cannot starve
+      attr[0].val.cooperative = 1;
+      cfg.attrs = attr;
+      cfg.numAttrs = 1;
+      {
+        ProfScope prof(ctx, B200MOE_KERNEL_TOKEN, st);
+        cudaLaunchKernelEx(&cfg, kn, p, tab);
+      }
+      return post_launch(ctx, "moe_token_kernel");
+    }
+  });
+}
+
 // route_first: the ids / scores buffers are OUTPUTS of the router, which this call launches first (fused entry).
 static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const int64_t* ids, const void* scores,
                        int scores_dtype, const int32_t* expert_slot, const int32_t* order, const void* residual,
@@ -931,6 +993,10 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   pp.ids64 = ids; pp.T = T; pp.K = c.top_k; pp.E = E;
   pp.offsets = ctx->offsets; pp.sorted_pair = ctx->sorted_pair; pp.inv = ctx->inv;
   pp.act_list = ctx->act_list; pp.n_act = ctx->n_act; pp.status = ctx->status;
+  if (route_first && T == 1 && ffn_kind == B200MOE_FFN_AUTO && ctx->token_kernel) {
+    rc = launch_token(ctx, layer, route_x ? route_x : x, const_cast<int64_t*>(ids), const_cast<void*>(scores), residual, out, pp, tab, norm, st);
+    if (rc != B200MOE_E_UNSUPPORTED) return rc;
+  }
   const bool fused_grouping = route_first && T * c.top_k <= kFusePermuteMaxPairs;
   if (route_first &&
       (rc = launch_router(ctx, layer, route_x ? route_x : x, nullptr, T, const_cast<int64_t*>(ids), const_cast<void*>(scores), nullptr, st,
@@ -1440,6 +1506,12 @@ extern "C" int b200moe_profile_read(b200moe_ctx* ctx, float* total_ms, int32_t* 
   return rc;
 }
 
+extern "C" int b200moe_set_token_kernel(b200moe_ctx* ctx, int enable) {
+  if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_set_token_kernel: null context");
+  ctx->token_kernel = enable != 0;
+  return B200MOE_OK;
+}
+
 extern "C" int b200moe_status(b200moe_ctx* ctx, int* device_status_out, void* stream) {
   if (!ctx || !device_status_out) return fail(ctx, B200MOE_E_ARG, "b200moe_status: null argument");
   CUDA_TRY(ctx, cudaSetDevice(ctx->cfg.device));
@@ -1448,6 +1520,8 @@ extern "C" int b200moe_status(b200moe_ctx* ctx, int* device_status_out, void* st
   CUDA_TRY(ctx, cudaMemcpyAsync(&v, ctx->status, sizeof v, cudaMemcpyDeviceToHost, st));
   CUDA_TRY(ctx, cudaMemsetAsync(ctx->status, 0, sizeof v, st));
   CUDA_TRY(ctx, cudaStreamSynchronize(st));
+  if (v & B200MOE_DEV_WAIT_EXPIRED)   // a grid barrier that gave up leaves its word between two states
+    CUDA_TRY(ctx, cudaMemsetAsync(ctx->tile_counter + ctx->cfg.max_tokens + 1, 0, sizeof(unsigned), st));
   *device_status_out = v;
   if (v) return fail(ctx, B200MOE_E_DEVICE, "device status word = %d", v);
   return B200MOE_OK;

@@ -327,6 +327,11 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
       for (int c0 = 0; c0 < n && ok; c0 += NMAX) {
         int kb = first;
         __nv_bfloat16 sv = sc[min(kb, nkb - 1)];
+        // Software pipeline over this group's stages: the tensor-memory stores of a stage are left in flight while
+        // the next stage's packed tile is fetched and its first half converted; only then does the group wait for
+        // the stores and hand the earlier stage to the MMA issuers (tcgen05.wait::st covers every store issued so far).
+        bool pending = false;
+        int pend_as = 0;
         for (; kb < nkb; kb += kI4uDeqGroups, gi += kI4uDeqGroups) {
           const __nv_bfloat16 sv_next = sc[min(kb + kI4uDeqGroups, nkb - 1)];   // the scale of this group's next stage is fetched a stage ahead
           const int ws = gi % WSTAGES, as = gi % STAGES;
@@ -340,7 +345,6 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
           if (lane == 0) mbar_arrive(&w_empty[ws]);
           const __nv_bfloat162 s2 = __nv_bfloat162(sv, sv);
           const uint32_t a_addr = a_addr0 + (uint32_t)(as * kI4uACols);
-          bool free_checked = false;
 #pragma unroll
           for (int half = 0; half < 2; ++half) {  // 64 k = 32 columns at a time keeps the register count down
             const uint32_t words[8] = {pk[2 * half].x, pk[2 * half].y, pk[2 * half].z, pk[2 * half].w,
@@ -352,18 +356,27 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
               i4u_dequant8(words[c], s2, o4);
               o[4 * c + 0] = o4[0]; o[4 * c + 1] = o4[1]; o[4 * c + 2] = o4[2]; o[4 * c + 3] = o4[3];
             }
-            if (!free_checked) {
+            if (half == 0) {
+              if (pending) {                      // the previous stage's stores have had a conversion's worth of time to land
+                tc_wait_st();
+                tc_fence_before();
+                if (lane == 0) mbar_arrive(&full[pend_as]);
+                pending = false;
+              }
               if (!__all_sync(0xffffffffu, wait_or_abort(&empty[as], aph ^ 1, abort_flag))) { ok = false; break; }
               tc_fence_after();
-              free_checked = true;
             }
             tc_st32(a_addr + (uint32_t)(half * 32), o);
           }
           if (!ok) break;
+          pending = true;
+          pend_as = as;
+          sv = sv_next;
+        }
+        if (pending) {                            // last stage of the job for this group: hand it over now
           tc_wait_st();
           tc_fence_before();
-          if (lane == 0) mbar_arrive(&full[as]);
-          sv = sv_next;
+          if (lane == 0) mbar_arrive(&full[pend_as]);
         }
         first = kb - nkb;                         // the stride carries over into the next job
       }

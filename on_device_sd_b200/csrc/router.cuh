@@ -181,9 +181,12 @@ template <typename T> __device__ __forceinline__ float boundary_distance(float s
   }
 }
 
-// One warp turns the E logits of token t into ordered top-k ids and softmax scores.
+// One warp turns the E logits of token t into ordered top-k ids and softmax scores.  ids_s / w_s (shared memory,
+// K entries; the score as the model dtype holds it) receive a private copy for a caller that goes on to use the
+// routing itself; write_global = false keeps the ids / scores / bitmap buffers untouched.
 template <typename T>
-__device__ void topk_softmax_token(const RouterParams& p, int t, int lane, float* skey, int* sidx) {
+__device__ void topk_softmax_token(const RouterParams& p, int t, int lane, float* skey, int* sidx, int* ids_s = nullptr,
+                                   float* w_s = nullptr, bool write_global = true) {
   constexpr int kMaxJ = kMaxExperts / 32;
   const int E = p.E, K = p.K;
   const int nj = (E + 31) / 32;
@@ -272,9 +275,12 @@ __device__ void topk_softmax_token(const RouterParams& p, int t, int lane, float
   for (int o = width >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   if (lane < K) {
     const float sc = ex / sum;
-    p.ids64[(size_t)t * K + lane] = idx;
-    reinterpret_cast<T*>(p.scores)[(size_t)t * K + lane] = Elem<T>::from_float(sc);
-    if (p.bitmap != nullptr) atomicOr(p.bitmap + (idx >> 6), 1ull << (idx & 63));
+    if (write_global) {
+      p.ids64[(size_t)t * K + lane] = idx;
+      reinterpret_cast<T*>(p.scores)[(size_t)t * K + lane] = Elem<T>::from_float(sc);
+      if (p.bitmap != nullptr) atomicOr(p.bitmap + (idx >> 6), 1ull << (idx & 63));
+    }
+    if (ids_s != nullptr) { ids_s[lane] = idx; w_s[lane] = rn<T>(sc); }
   }
 }
 

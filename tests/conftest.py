@@ -71,5 +71,5 @@ def ulp_tolerance(dtype: torch.dtype) -> float:
     return {torch.float32: 1e-6, torch.float16: 2.0 ** -11, torch.bfloat16: 2.0 ** -8}[dtype]
 
 
-# BASELINE tolerances for low-precision outputs: max-abs 2e-2, mean-rel 5e-3 (mean|a-b| / mean|b|)
+# tolerances of the path for low-precision outputs: max-abs 2e-2, mean-rel 5e-3 (mean|a-b| / mean|b|)
 OUT_TOL = {torch.float32: (1e-5, 1e-5), torch.float16: (2e-2, 5e-3), torch.bfloat16: (2e-2, 5e-3)}

@@ -191,7 +191,7 @@ def _device_oracle(L, ids, scores, order):
 
 @pytest.mark.parametrize("name,T", [("qwen3", 256), ("qwen3", 8), ("mixtral", 64), ("mixtral", 1), ("mixtral", 16)])
 def test_full_size_against_device_run_of_oracle(name, T):
-    """BASELINE's full sizes: inputs drawn on the GPU, the oracle's functions evaluated on those
+    """The benchmark configurations at their full sizes: inputs drawn on the GPU, the oracle's functions evaluated on those
     CUDA tensors (torch eager = the reference's arithmetic on this device), same tolerance."""
     from on_device_sd_b200.synth import make_named
     L = make_named(name, T, device="cuda", gen_device="cuda")
