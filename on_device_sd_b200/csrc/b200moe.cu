@@ -926,7 +926,7 @@ static int launch_token(b200moe_ctx* ctx, int layer, const void* x, int64_t* ids
     p.r.normed_out = norm->normed_out; p.r.res_out = norm->res_out;
   }
   p.experts = ctx->d_experts + (size_t)layer * c.num_experts;
-  p.h = ctx->h; p.y = ctx->y; p.residual = residual; p.out = out; p.I = c.intermediate_size;
+  p.h = ctx->h; p.residual = residual; p.out = out; p.I = c.intermediate_size;
   p.gbar = ctx->tile_counter + c.max_tokens + 1;
   p.status = ctx->status;
   p.wait_cycles = 1ll << 31;
@@ -1505,6 +1505,10 @@ extern "C" int b200moe_profile_read(b200moe_ctx* ctx, float* total_ms, int32_t* 
   ctx->prof.clear();
   return rc;
 }
+
+#ifdef B200MOE_TOKEN_TRACE
+extern "C" int b200moe_token_trace(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_token_trace, 32 * sizeof(unsigned long long)); }
+#endif
 
 extern "C" int b200moe_set_token_kernel(b200moe_ctx* ctx, int enable) {
   if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_set_token_kernel: null context");

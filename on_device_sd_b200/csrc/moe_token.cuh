@@ -9,9 +9,10 @@
 // measured copy rate) and a chain of four dependent kernels spends more than that on its hand-overs.  Here one
 // persistent CTA per SM keeps per-warp rings of 1-D bulk copies (the GEMV kernel's scheme) running ACROSS the
 // phases: weights do not depend on activations, so while a warp waits at the grid barrier for h to be complete
-// its first down-projection rows are already on their way into shared memory.  The three grid barriers are
-// sense-reversing counters in global memory with a bounded wait; the launch is cooperative, so every CTA is
-// resident and the barriers cannot starve.
+// its first down-projection rows are already on their way into shared memory.  The down projection's unit is a
+// pair of output rows over ALL chosen experts, so the warp that computed a row's K products also runs the combine
+// for it and no third hand-over is needed.  The two grid barriers (logits complete, h complete) are counters in
+// global memory with a bounded wait; the launch is cooperative, so every CTA is resident and they cannot starve.
 #pragma once
 #include "common.cuh"
 #include "ffn_gemv.cuh"
@@ -25,7 +26,6 @@ struct TokenParams {
   RouterParams r;              // x, wg, bias, logits, ids64, scores, H, E, K (T = 1); r.perm = tables of the grouping
   const ExpertPtrs* experts;   // table of this layer, [E]
   void* h;                     // [K][I] silu(gate) * up, one row per live slot of the token
-  void* y;                     // [K][H] expert outputs, same rows
   const void* residual;        // [H] or null (with the fused norm: r.res_out)
   void* out;                   // [H]
   int I;
@@ -62,6 +62,7 @@ __device__ __forceinline__ bool grid_barrier_bounded(unsigned* bar, long long li
   return *s_flag != 0;
 }
 
+
 constexpr int kTokenMaxRowBytes = 16384;   // the token row kept in shared memory beside the rings
 
 template <typename S> constexpr size_t token_smem_bytes() { return S::SMEM + kTokenMaxRowBytes; }
@@ -75,8 +76,7 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
   constexpr int CB = 8 * (int)sizeof(T);                 // bytes of one 8-element chunk
   constexpr int SEG_ELEMS = SEG / (int)sizeof(T);
   extern __shared__ __align__(128) unsigned char smem_raw[];
-  __shared__ float skey[32];
-  __shared__ int sidx[32];
+  __shared__ TopkSmem<1> s_topk;
   __shared__ int s_ids[kMaxTopK];
   __shared__ float s_w[kMaxTopK];
   __shared__ int s_live[kMaxTopK];       // live index j -> slot k of the token
@@ -84,7 +84,6 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
   __shared__ const unsigned char* s_wp[3][kMaxTopK];
   __shared__ int s_nlive;
   __shared__ int s_flag;
-  __shared__ int s_perm[kRouterFuseSmemInts];
   __shared__ float s_part[kNormThreads / 32];
   __shared__ float s_scale;
   static_assert(kNormThreads == S::THREADS, "rmsnorm_row is written for this CTA size");
@@ -96,6 +95,7 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
   const int H = p.r.H, E = p.r.E, K = p.r.K, I = p.I;
   const int nch = H / 8;
 
+  TOKEN_TRACE(0);
   // ---- phase 0: the token row into shared memory, one warp per gate row ----
   if (p.r.norm_w != nullptr) {
     // the norm in front of the block (RouterParams): every CTA normalises the row for itself, CTA 0 publishes it
@@ -150,80 +150,129 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
     if (p.r.bias != nullptr) l = rn<T>(l + Elem<T>::to_float(reinterpret_cast<const T*>(p.r.bias)[e]));
     if (lane == 0) p.r.logits[e] = l;
   }
+  TOKEN_TRACE(1);
   bool alive = grid_barrier_bounded(p.gbar, p.wait_cycles, &s_flag, p.status);
+  TOKEN_TRACE(2);
 
   // ---- phase 1: every CTA selects the experts for itself; CTA 0 publishes ids, scores and the grouping ----
-  if (alive && warp == 0) topk_softmax_token<T>(p.r, 0, lane, skey, sidx, s_ids, s_w, blockIdx.x == 0);
-  __syncthreads();
-  if (threadIdx.x == 0) {
+  if (alive) topk_softmax_tile<T, 1>(topk_args(p.r), 0, 1, &s_topk, s_ids, s_w, blockIdx.x == 0);
+  TOKEN_TRACE(9);
+  if (warp == 0) {
     int n = 0;
     if (alive) {
-      for (int k = 0; k < K; ++k) {
-        const int e = s_ids[k];
-        const int slot = (e >= 0 && e < E) ? st.slot[e] : -1;
-        if (slot < 0) continue;                       // no weights for this expert in the placement: skipped
-        const ExpertPtrs ep = p.experts[slot];
-        s_live[n] = k;
-        s_wp[0][n] = reinterpret_cast<const unsigned char*>(ep.w[0]);
-        s_wp[1][n] = reinterpret_cast<const unsigned char*>(ep.w[1]);
-        s_wp[2][n] = reinterpret_cast<const unsigned char*>(ep.w[2]);
-        int i = n;
-        while (i > 0 && st.rank[s_ids[s_live[s_order[i - 1]]]] > st.rank[e]) {   // stable insertion by rank
-          s_order[i] = s_order[i - 1];
-          --i;
+      __syncwarp();
+      // lane k looks after slot k of the token: the K table entries are fetched side by side, not one after the other
+      int slot = -1, e = -1;
+      if (lane < K) {
+        e = s_ids[lane];
+        slot = (e >= 0 && e < E) ? st.slot[e] : -1;   // no weights for this expert in the placement: skipped
+      }
+      ExpertPtrs ep{};
+      if (slot >= 0) ep = p.experts[slot];
+      const unsigned live = __ballot_sync(0xffffffffu, slot >= 0);
+      n = __popc(live);
+      if (slot >= 0) {
+        const int j = __popc(live & ((1u << lane) - 1u));
+        s_live[j] = lane;
+        s_wp[0][j] = reinterpret_cast<const unsigned char*>(ep.w[0]);
+        s_wp[1][j] = reinterpret_cast<const unsigned char*>(ep.w[1]);
+        s_wp[2][j] = reinterpret_cast<const unsigned char*>(ep.w[2]);
+        // position in the combine's accumulation order: by rank, equal ranks in slot order
+        const int my_rank = st.rank[e];
+        int before = 0;
+        for (int k2 = 0; k2 < K; ++k2) {
+          if (!((live >> k2) & 1u) || k2 == lane) continue;
+          const int r2 = st.rank[s_ids[k2]];
+          before += (r2 < my_rank || (r2 == my_rank && k2 < lane)) ? 1 : 0;
         }
-        s_order[i] = n;
-        ++n;
+        s_order[before] = j;
       }
     }
-    s_nlive = n;
+    if (lane == 0) s_nlive = n;
   }
   __syncthreads();
-  if (alive && blockIdx.x == 0) permute_block(p.r.perm, st, s_perm);
+  TOKEN_TRACE(11);
+  if (alive && blockIdx.x == 0) {
+    // The grouping tables of this one-token batch, for readers of the last call's grouping (what permute_block
+    // leaves): the K pairs in expert order, every id valid and distinct because the top-k above produced them.
+    const PermuteParams& t = p.r.perm;
+    for (int e = threadIdx.x; e <= E; e += S::THREADS) {
+      int c = 0;
+      for (int k = 0; k < K; ++k) c += (s_ids[k] < e) ? 1 : 0;
+      t.offsets[e] = c;
+    }
+    if (threadIdx.x < K) {
+      const int k = threadIdx.x, e = s_ids[k];
+      const bool served = st.slot[e] >= 0;
+      int pos = 0, act_pos = 0;
+      for (int k2 = 0; k2 < K; ++k2) {
+        const int e2 = s_ids[k2];
+        pos += (e2 < e) ? 1 : 0;
+        act_pos += (e2 < e && st.slot[e2] >= 0) ? 1 : 0;
+      }
+      t.inv[k] = pos;
+      t.sorted_pair[pos] = k;
+      if (served) t.act_list[act_pos] = e;
+    }
+    if (threadIdx.x == 0) *t.n_act = s_nlive;
+  }
 
+  TOKEN_TRACE(3);
   // ---- phases 2 and 3 share one list of units and one ring per warp ----
   const int n_live = s_nlive;
-  const int gw = blockIdx.x * S::WARPS + warp;
+  // warp-major: when the units do not divide evenly, the extra ones fall on ONE warp of many SMs, not on every warp of a few
+  const int gw = warp * (int)gridDim.x + blockIdx.x;
   const int W = gridDim.x * S::WARPS;
   const int half_I = I / 2;
-  const int U2 = n_live * half_I;                       // gate/up: rows (r, r+1) of gate_proj and of up_proj
-  // down projection: one row split into four K quarters when four-row units would leave warps idle (and a
-  // quarter still fills a ring segment), else rows (r .. r+3)
-  const bool quarter = (I % 32 == 0) && I * (int)sizeof(T) >= 4 * SEG && n_live * (H / 4) < 6 * W;
-  const int groups3 = quarter ? H : H / 4;
-  const int total_units = U2 + n_live * groups3;
+  const int U2 = n_live * half_I;                       // gate/up: rows (r, r+1) of gate_proj and of up_proj of one expert
+  // down projection + combine: rows (r, r+1) of down_proj of EVERY live expert, two experts per stage in the
+  // combine's accumulation order, so that the warp holding a row's K products also adds them up
+  const int U3 = n_live > 0 ? H / 2 : 0;
+  const int npair = (n_live + 1) / 2;
+  const int total_units = U2 + U3;
   const int rb2 = H * (int)sizeof(T), nseg2 = (rb2 + SEG - 1) / SEG;
-  const int rb3 = (quarter ? I / 4 : I) * (int)sizeof(T), nseg3 = (rb3 + SEG - 1) / SEG;
+  const int rb3 = I * (int)sizeof(T), nseg3 = (rb3 + SEG - 1) / SEG;
   const uint64_t policy = l2_policy_evict_first();
   const int sidx4 = lane & 3;
 
   // producer: STAGES-1 stages ahead of the consumer, across unit and phase boundaries
   int pu = gw, ps = 0, issued = 0;
-  const unsigned char* prow = nullptr;
-  int p_nseg = 0, p_rb = 0;
+  const unsigned char* prow = nullptr;     // gate/up unit: this lane's row
+  int p_row3 = 0;                          // down unit: this lane's row index
+  int p_nstage = 0;
   auto open_unit = [&](int u) {
     if (u < U2) {
       const int j = u / half_I, r0 = (u - j * half_I) * 2;
       prow = s_wp[sidx4 >> 1][j] + (size_t)(r0 + (sidx4 & 1)) * rb2;
-      p_nseg = nseg2; p_rb = rb2;
+      p_nstage = nseg2;
     } else {
-      const int v = u - U2;
-      const int j = v / groups3, g = v - j * groups3;
-      if (quarter) prow = s_wp[2][j] + (size_t)g * I * sizeof(T) + (size_t)sidx4 * rb3;
-      else prow = s_wp[2][j] + (size_t)(g * 4 + sidx4) * rb3;
-      p_nseg = nseg3; p_rb = rb3;
+      p_row3 = (u - U2) * 2 + (sidx4 & 1);
+      p_nstage = npair * nseg3;
     }
   };
   if (alive && pu < total_units) open_unit(pu);
   auto produce = [&]() {
     if (pu >= total_units) return;
     const int slot = issued % STAGES;
-    const uint32_t bytes = (uint32_t)min(SEG, p_rb - ps * SEG);
-    if (lane == 0) mbar_expect_tx(&full[slot], 4 * bytes);
+    const unsigned char* src;
+    uint32_t bytes, streams = 4;
+    bool mine = true;
+    if (pu < U2) {
+      bytes = (uint32_t)min(SEG, rb2 - ps * SEG);
+      src = prow + (size_t)ps * SEG;
+    } else {
+      const int q = ps / nseg3, seg = ps - q * nseg3;
+      const int ord = 2 * q + (sidx4 >> 1);             // streams 0,1: expert 2q of the order; streams 2,3: expert 2q+1
+      if (2 * q + 1 >= n_live) streams = 2;
+      mine = ord < n_live;
+      bytes = (uint32_t)min(SEG, rb3 - seg * SEG);
+      src = s_wp[2][s_order[min(ord, n_live - 1)]] + (size_t)p_row3 * rb3 + (size_t)seg * SEG;
+    }
+    if (lane == 0) mbar_expect_tx(&full[slot], streams * bytes);
     __syncwarp();
-    if (lane < 4) bulk_g2s(ring + (size_t)(slot * 4 + lane) * SEG, prow + (size_t)ps * SEG, bytes, &full[slot], policy);
+    if (lane < 4 && mine) bulk_g2s(ring + (size_t)(slot * 4 + lane) * SEG, src, bytes, &full[slot], policy);
     ++issued;
-    if (++ps == p_nseg) {
+    if (++ps == p_nstage) {
       pu += W;
       ps = 0;
       if (pu < total_units) open_unit(pu);
@@ -238,7 +287,7 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
 
   int consumed = 0;
   bool dead = !alive;
-  // waits for the next stage of this warp's ring; false when the wait ran out
+  // waits for the next stage of this warp's ring; null when the wait ran out
   auto next_stage = [&]() -> const unsigned char* {
     produce();
     const int slot = consumed % STAGES;
@@ -287,37 +336,42 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
       reinterpret_cast<T*>(p.h)[(size_t)j * I + r0 + lane] = Elem<T>::from_float(__fmul_rn(sg, u));
     }
   }
+  TOKEN_TRACE(4);
   if (!grid_barrier_bounded(p.gbar, p.wait_cycles, &s_flag, p.status)) dead = true;     // h is complete
+  TOKEN_TRACE(5);
 
   for (; cu < total_units && !dead; cu += W) {
-    const int v = cu - U2;
-    const int j = v / groups3, g = v - j * groups3;
-    const T* hrow = reinterpret_cast<const T*>(p.h) + (size_t)j * I;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    for (int seg = 0; seg < nseg3; ++seg) {
-      const unsigned char* sbase = next_stage();
-      if (sbase == nullptr) break;
-      const int nchunk = min(SEG, rb3 - seg * SEG) / CB;
-      for (int cl = lane; cl < nchunk; cl += 32) {
-        if (quarter) {
+    const int r0 = (cu - U2) * 2;
+    float out_acc[2] = {0.0f, 0.0f};     // the combine's running sums of rows r0, r0+1, each held as the model dtype holds it
+    for (int q = 0; q < npair && !dead; ++q) {
+      const int ja = s_order[2 * q];
+      const bool two = 2 * q + 1 < n_live;
+      const int jb = s_order[two ? 2 * q + 1 : 2 * q];
+      const T* ha = reinterpret_cast<const T*>(p.h) + (size_t)ja * I;
+      const T* hb = reinterpret_cast<const T*>(p.h) + (size_t)jb * I;
+      float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+      for (int seg = 0; seg < nseg3; ++seg) {
+        static_assert(SEG / CB == 32 * 4, "one h chunk per lane and quarter of a segment");
+        const int nchunk = min(SEG, rb3 - seg * SEG) / CB;
+        // h was written in this launch: plain loads (L2 for the most part - the rings leave little L1), all of the
+        // segment's chunks requested before the wait for the weights
+        Chunk<T> hca[4], hcb[4];
 #pragma unroll
-          for (int s = 0; s < 4; ++s) {
-            Chunk<T> wc, hc;
-            wc.from_smem(sbase + (size_t)s * SEG + (size_t)cl * CB);
-            hc.from_smem(hrow + (size_t)s * (I / 4) + (size_t)seg * SEG_ELEMS + (size_t)cl * 8);   // plain load: written in this launch
-            float wf[8], hf[8];
-            wc.unpack(wf);
-            hc.unpack(hf);
-#pragma unroll
-            for (int i = 0; i < 8; ++i) acc[s] = fmaf(wf[i], hf[i], acc[s]);
+        for (int u = 0; u < 4; ++u)
+          if (lane + 32 * u < nchunk) {
+            hca[u].from_smem(ha + (size_t)seg * SEG_ELEMS + (size_t)(lane + 32 * u) * 8);
+            hcb[u].from_smem(hb + (size_t)seg * SEG_ELEMS + (size_t)(lane + 32 * u) * 8);
           }
-        } else {
-          Chunk<T> hc;
-          hc.from_smem(hrow + (size_t)seg * SEG_ELEMS + (size_t)cl * 8);
-          float hf[8];
-          hc.unpack(hf);
+        const unsigned char* sbase = next_stage();
+        if (sbase == nullptr) break;
 #pragma unroll
-          for (int s = 0; s < 4; ++s) {
+        for (int u = 0; u < 4; ++u) {
+          const int cl = lane + 32 * u;
+          if (cl >= nchunk) break;
+          float hf[8];
+          hca[u].unpack(hf);
+#pragma unroll
+          for (int s = 0; s < 2; ++s) {
             Chunk<T> wc;
             wc.from_smem(sbase + (size_t)s * SEG + (size_t)cl * CB);
             float wf[8];
@@ -325,58 +379,51 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
 #pragma unroll
             for (int i = 0; i < 8; ++i) acc[s] = fmaf(wf[i], hf[i], acc[s]);
           }
+          if (two) {
+            hcb[u].unpack(hf);
+#pragma unroll
+            for (int s = 2; s < 4; ++s) {
+              Chunk<T> wc;
+              wc.from_smem(sbase + (size_t)s * SEG + (size_t)cl * CB);
+              float wf[8];
+              wc.unpack(wf);
+#pragma unroll
+              for (int i = 0; i < 8; ++i) acc[s] = fmaf(wf[i], hf[i], acc[s]);
+            }
+          }
         }
+        __syncwarp();
       }
-      __syncwarp();
+      if (dead) break;
+#pragma unroll
+      for (int s = 0; s < 4; ++s) acc[s] = warp_sum(acc[s]);       // every lane holds the four sums
+      // the expert's output rounded as F.linear rounds it, times its score, added in rank order: the rounding
+      // points of `final_output[tok] += expert_output * weights`
+      const float wa = s_w[s_live[ja]], wb = s_w[s_live[jb]];
+#pragma unroll
+      for (int rr = 0; rr < 2; ++rr) {
+        out_acc[rr] = rn<T>(__fadd_rn(out_acc[rr], rn<T>(__fmul_rn(rn<T>(acc[rr]), wa))));
+        if (two) out_acc[rr] = rn<T>(__fadd_rn(out_acc[rr], rn<T>(__fmul_rn(rn<T>(acc[2 + rr]), wb))));
+      }
     }
     if (dead) break;
-    if (quarter) {
-      const float s = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
-      if (lane == 0) reinterpret_cast<T*>(p.y)[(size_t)j * H + g] = Elem<T>::from_float(s);
-    } else {
-#pragma unroll
-      for (int s = 0; s < 4; ++s) acc[s] = warp_sum(acc[s]);
-      if (lane < 4) {
-        const float s = lane == 0 ? acc[0] : lane == 1 ? acc[1] : lane == 2 ? acc[2] : acc[3];
-        reinterpret_cast<T*>(p.y)[(size_t)j * H + g * 4 + lane] = Elem<T>::from_float(s);
-      }
+    if (lane < 2) {
+      float o = lane == 0 ? out_acc[0] : out_acc[1];
+      if (p.residual != nullptr)      // plain load: with the fused norm CTA 0 wrote it in this launch
+        o = rn<T>(__fadd_rn(Elem<T>::to_float(reinterpret_cast<const T*>(p.residual)[r0 + lane]), o));
+      reinterpret_cast<T*>(p.out)[r0 + lane] = Elem<T>::from_float(o);
     }
   }
-  if (!grid_barrier_bounded(p.gbar, p.wait_cycles, &s_flag, p.status)) dead = true;     // y is complete
-
-  // ---- phase 4: out = residual + sum over the live experts, in rank order, rounded where the reference rounds ----
-  if (!dead && warp == 0) {
-    const T* y = reinterpret_cast<const T*>(p.y);
-    for (int c = blockIdx.x * 32 + lane; c < nch; c += (int)gridDim.x * 32) {
-      float acc[8];
-#pragma unroll
-      for (int i = 0; i < 8; ++i) acc[i] = 0.0f;
-      for (int j0 = 0; j0 < n_live; j0 += 8) {
-        Chunk<T> yc[8];
-#pragma unroll
-        for (int u = 0; u < 8; ++u)
-          if (j0 + u < n_live) yc[u].from_smem(y + (size_t)s_order[j0 + u] * H + (size_t)c * 8);
-#pragma unroll
-        for (int u = 0; u < 8; ++u) {
-          if (j0 + u >= n_live) break;
-          const float w = s_w[s_live[s_order[j0 + u]]];
-          float yf[8];
-          yc[u].unpack(yf);
-#pragma unroll
-          for (int i = 0; i < 8; ++i) acc[i] = rn<T>(__fadd_rn(acc[i], rn<T>(__fmul_rn(yf[i], w))));
-        }
-      }
-      if (p.residual != nullptr) {
-        Chunk<T> rc;
-        rc.from_smem(reinterpret_cast<const T*>(p.residual) + (size_t)c * 8);    // plain load: with the fused norm CTA 0 wrote it in this launch
-        float rf[8];
-        rc.unpack(rf);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) acc[i] = rn<T>(__fadd_rn(rf[i], acc[i]));
-      }
-      store_chunk<T>(reinterpret_cast<T*>(p.out) + (size_t)c * 8, acc);
+  TOKEN_TRACE(6);
+  if (n_live == 0 && !dead) {
+    // nothing served: the block contributes zeros
+    for (int c = blockIdx.x * S::THREADS + threadIdx.x; c < H; c += (int)gridDim.x * S::THREADS) {
+      float o = 0.0f;
+      if (p.residual != nullptr) o = rn<T>(__fadd_rn(Elem<T>::to_float(reinterpret_cast<const T*>(p.residual)[c]), o));
+      reinterpret_cast<T*>(p.out)[c] = Elem<T>::from_float(o);
     }
   }
+  TOKEN_TRACE(8);
   if (dead) {
     // A wait ran out.  Copies issued earlier may still be in flight towards this warp's ring: give each of them
     // a short, bounded chance to land before the shared memory can pass to another CTA.

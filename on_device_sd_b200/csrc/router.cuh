@@ -181,12 +181,148 @@ template <typename T> __device__ __forceinline__ float boundary_distance(float s
   }
 }
 
-// One warp turns the E logits of token t into ordered top-k ids and softmax scores.  ids_s / w_s (shared memory,
-// K entries; the score as the model dtype holds it) receive a private copy for a caller that goes on to use the
-// routing itself; write_global = false keeps the ids / scores / bitmap buffers untouched.
+// Top-k / softmax of up to TT tokens by ALL kRouterThreads threads of a CTA (it synchronises).
+//
+// Shaped by what this code costs where it runs - once per launch, on the critical path, with cold instruction
+// caches and one or a few warps: a straight-line, unrolled one-warp version measured 13 - 24 us per call against
+// 4 - 5 us for the same code once resident, and a single warp retires an instruction only every ~7 cycles.  So the
+// loops are rolled, the function is not inlined, the O(E^2) part is spread over the whole CTA and the 32-slot
+// network runs only for tokens that need it:
+//   A  every thread copies logits into shared memory (NaN sorts first, as torch.topk has it);
+//   B  one thread per (token, expert) counts the entries ahead of its own in (value descending, index ascending)
+//      order - its rank; ranks below k are the kept entries, written to slot `rank` of the token's list;
+//   C  warp tt finishes token tt.  With k distinct kept values the descending order IS the result (a sorting
+//      network sorts any arrangement of distinct keys to the same order).  With equal values among them the
+//      order of the equal ones is whatever torch's CUDA kernel makes of it: the kept entries are arranged as that
+//      kernel gathers them (entries > kth in index order, then entries == kth in index order) and passed through
+//      the 32-slot bitonic network it applies for 1 < k <= 32.  Then the softmax over the k kept logits.
+constexpr int kTopkLogSlots = kMaxExperts + 4;
+template <int TT> struct TopkSmem {
+  __align__(16) float log[TT][kTopkLogSlots];
+  float sel_v[TT][32];
+  int sel_i[TT][32];
+  float key[TT][32];
+  int idx[TT][32];
+};
+struct TopkArgs {          // by value: passing the kernel's parameter struct by reference would put a copy on the stack
+  const void* logits_in;   // [T,E] model dtype, or null
+  const float* logits;     // [T,E] fp32
+  int64_t* ids64;
+  void* scores;
+  unsigned long long* bitmap;
+  int E, K;
+};
+__device__ __forceinline__ TopkArgs topk_args(const RouterParams& p) {
+  return TopkArgs{p.logits_in, p.logits, p.ids64, p.scores, p.bitmap, p.E, p.K};
+}
+
+// ids_s / w_s (shared memory, K entries; the score as the model dtype holds it) receive a private copy of token
+// t0's routing for a caller that goes on to use it; write_global = false leaves ids / scores / bitmap untouched.
+template <typename T, int TT>
+__device__ __noinline__ void topk_softmax_tile(TopkArgs a, int t0, int ntok, TopkSmem<TT>* sm, int* ids_s, float* w_s, bool write_global) {
+  static_assert(TT <= kRouterThreads / 32, "one warp per token in the last step");
+  const int E = a.E, K = a.K;
+  const int E4 = (E + 3) & ~3;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+#pragma unroll 1
+  for (int i = tid; i < ntok * E4; i += kRouterThreads) {
+    const int tt = i / E4, e = i - tt * E4;
+    float v = -INFINITY;                                  // padding up to a multiple of four never wins a comparison
+    if (e < E) {
+      const size_t at = (size_t)(t0 + tt) * E + e;
+      v = a.logits_in != nullptr ? Elem<T>::to_float(reinterpret_cast<const T*>(a.logits_in)[at]) : __ldcg(a.logits + at);
+      if (v != v) v = INFINITY;
+    }
+    sm->log[tt][e] = v;
+  }
+  __syncthreads();
+#pragma unroll 1
+  for (int i = tid; i < ntok * E; i += kRouterThreads) {
+    const int tt = i / E, e = i - tt * E;
+    const float* row = sm->log[tt];
+    const float v = row[e];
+    int cnt = 0;
+#pragma unroll 1
+    for (int o = 0; o < E4; o += 4) {
+      const float4 w = *reinterpret_cast<const float4*>(row + o);
+      cnt += (w.x > v || (w.x == v && o < e)) ? 1 : 0;
+      cnt += (w.y > v || (w.y == v && o + 1 < e)) ? 1 : 0;
+      cnt += (w.z > v || (w.z == v && o + 2 < e)) ? 1 : 0;
+      cnt += (w.w > v || (w.w == v && o + 3 < e)) ? 1 : 0;
+    }
+    if (cnt < K) { sm->sel_v[tt][cnt] = v; sm->sel_i[tt][cnt] = e; }
+  }
+  __syncthreads();
+  if (warp >= ntok) return;
+  const int tt = warp;
+  float key = (lane < K) ? sm->sel_v[tt][lane] : 0.0f;
+  int idx = (lane < K) ? sm->sel_i[tt][lane] : -1;
+  bool ok = lane < K;
+  const float below = __shfl_down_sync(0xffffffffu, key, 1);
+  if (__any_sync(0xffffffffu, lane + 1 < K && below == key)) {
+    const float kth = sm->sel_v[tt][K - 1];
+    if (lane < K) {
+      int gt_before = 0, eq_before = 0, gt_total = 0;
+#pragma unroll 1
+      for (int r = 0; r < K; ++r) {
+        const float w = sm->sel_v[tt][r];
+        const int wi = sm->sel_i[tt][r];
+        gt_total += (w > kth) ? 1 : 0;
+        gt_before += (w > kth && wi < idx) ? 1 : 0;
+        eq_before += (w == kth && wi < idx) ? 1 : 0;
+      }
+      const int pos = key > kth ? gt_before : gt_total + eq_before;
+      sm->key[tt][pos] = key;
+      sm->idx[tt][pos] = idx;
+    }
+    __syncwarp();
+    if (lane < K) { key = sm->key[tt][lane]; idx = sm->idx[tt][lane]; }
+    // sorting stages of size 2 .. 16 in alternating directions, then the merge of size 32 (its direction flag is clear)
+#pragma unroll 1
+    for (int size = 2; size <= 32; size <<= 1) {
+#pragma unroll 1
+      for (int stride = size >> 1; stride > 0; stride >>= 1) {
+        const bool flag = ((lane & ~stride) & size) != 0;
+        const float pk = __shfl_xor_sync(0xffffffffu, key, stride);
+        const int pi = __shfl_xor_sync(0xffffffffu, idx, stride);
+        const bool pok = __shfl_xor_sync(0xffffffffu, (int)ok, stride) != 0;
+        const bool is_lo = (lane & stride) == 0;
+        const float k_lo = is_lo ? key : pk, k_hi = is_lo ? pk : key;
+        const bool ok_lo = is_lo ? ok : pok, ok_hi = is_lo ? pok : ok;
+        const bool pred = (k_lo > k_hi && ok_lo) || !ok_hi;
+        if (pred == flag) { key = pk; idx = pi; ok = pok; }
+      }
+    }
+  }
+
+  // softmax over the k kept logits (fp32 math, butterfly reductions over next_pow2(k) lanes)
+  int width = 1;
+  while (width < K) width <<= 1;
+  float mx = (lane < K) ? key : -INFINITY;
+#pragma unroll 1
+  for (int o = width >> 1; o > 0; o >>= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, o));
+  const float ex = (lane < K) ? expf(key - mx) : 0.0f;
+  float sum = ex;
+#pragma unroll 1
+  for (int o = width >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
+  if (lane < K) {
+    const float sc = ex / sum;
+    const size_t at = (size_t)(t0 + tt) * K + lane;
+    if (write_global) {
+      a.ids64[at] = idx;
+      reinterpret_cast<T*>(a.scores)[at] = Elem<T>::from_float(sc);
+      if (a.bitmap != nullptr) atomicOr(a.bitmap + (idx >> 6), 1ull << (idx & 63));
+    }
+    if (ids_s != nullptr && tt == 0) { ids_s[lane] = idx; w_s[lane] = rn<T>(sc); }
+  }
+}
+
+// One warp turns the E logits of token t into ordered top-k ids and softmax scores: the same selection, placement,
+// network and softmax as topk_softmax_tile, kept in registers and unrolled.  This is the form for kernels that run
+// it many times per SM (token tiles of a large batch, caller-supplied logits), where the code is resident after the
+// first tile and one warp per token beats the CTA-wide counting; a launch that runs it once takes the tile form.
 template <typename T>
-__device__ void topk_softmax_token(const RouterParams& p, int t, int lane, float* skey, int* sidx, int* ids_s = nullptr,
-                                   float* w_s = nullptr, bool write_global = true) {
+__device__ void topk_softmax_token(const RouterParams& p, int t, int lane, float* skey, int* sidx) {
   constexpr int kMaxJ = kMaxExperts / 32;
   const int E = p.E, K = p.K;
   const int nj = (E + 31) / 32;
@@ -275,12 +411,9 @@ __device__ void topk_softmax_token(const RouterParams& p, int t, int lane, float
   for (int o = width >> 1; o > 0; o >>= 1) sum += __shfl_xor_sync(0xffffffffu, sum, o);
   if (lane < K) {
     const float sc = ex / sum;
-    if (write_global) {
-      p.ids64[(size_t)t * K + lane] = idx;
-      reinterpret_cast<T*>(p.scores)[(size_t)t * K + lane] = Elem<T>::from_float(sc);
-      if (p.bitmap != nullptr) atomicOr(p.bitmap + (idx >> 6), 1ull << (idx & 63));
-    }
-    if (ids_s != nullptr) { ids_s[lane] = idx; w_s[lane] = rn<T>(sc); }
+    p.ids64[(size_t)t * K + lane] = idx;
+    reinterpret_cast<T*>(p.scores)[(size_t)t * K + lane] = Elem<T>::from_float(sc);
+    if (p.bitmap != nullptr) atomicOr(p.bitmap + (idx >> 6), 1ull << (idx & 63));
   }
 }
 
@@ -298,8 +431,7 @@ template <typename T, int TT, int U, bool NORM = false> __global__ void __launch
   __shared__ int s_perm[kRouterFuseSmemInts];
   constexpr bool kExact = std::is_same<T, float>::value;
   using Acc = typename std::conditional<kExact, double, float>::type;
-  __shared__ float skey[TT][32];
-  __shared__ int sidx[TT][32];
+  __shared__ TopkSmem<TT> s_topk;
   __shared__ int s_last;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int t0 = blockIdx.x * TT;
@@ -391,7 +523,7 @@ template <typename T, int TT, int U, bool NORM = false> __global__ void __launch
   __syncthreads();
   if (!s_last) return;
   __threadfence();
-  if (warp < TT && t0 + warp < p.T) topk_softmax_token<T>(p, t0 + warp, lane, skey[warp], sidx[warp]);
+  topk_softmax_tile<T, TT>(topk_args(p), t0, min(TT, p.T - t0), &s_topk, nullptr, nullptr, true);
   if (p.fuse_permute) router_fused_tail(p, st, gridDim.x, s_perm);
   if (p.ep_dispatch) router_dispatch_tail<T>(p, peers, t0, min(TT, p.T - t0), gridDim.x);
 }
