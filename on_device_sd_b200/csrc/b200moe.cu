@@ -1506,10 +1506,6 @@ extern "C" int b200moe_profile_read(b200moe_ctx* ctx, float* total_ms, int32_t* 
   return rc;
 }
 
-#ifdef B200MOE_TOKEN_TRACE
-extern "C" int b200moe_token_trace(unsigned long long* out) { return (int)cudaMemcpyFromSymbol(out, g_token_trace, 32 * sizeof(unsigned long long)); }
-#endif
-
 extern "C" int b200moe_set_token_kernel(b200moe_ctx* ctx, int enable) {
   if (!ctx) return fail(nullptr, B200MOE_E_ARG, "b200moe_set_token_kernel: null context");
   ctx->token_kernel = enable != 0;

@@ -154,20 +154,6 @@ __device__ __forceinline__ bool ep_wait_flag(const unsigned* flag, unsigned epoc
   }
 }
 
-#ifdef B200MOE_TOKEN_TRACE
-__device__ unsigned long long g_token_trace[32];
-__device__ __forceinline__ void token_trace(int i) {
-  if (threadIdx.x == 0 && blockIdx.x < 2) {
-    unsigned long long t;
-    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
-    g_token_trace[blockIdx.x * 16 + i] = t;
-  }
-}
-#define TOKEN_TRACE(i) token_trace(i)
-#else
-#define TOKEN_TRACE(i)
-#endif
-
 // Device status word bits (mirrors B200MOE_DEV_* of the public header).
 constexpr int kDevBadExpertId = 1;
 constexpr int kDevBadOffsets = 2;

@@ -95,7 +95,6 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
   const int H = p.r.H, E = p.r.E, K = p.r.K, I = p.I;
   const int nch = H / 8;
 
-  TOKEN_TRACE(0);
   // ---- phase 0: the token row into shared memory, one warp per gate row ----
   if (p.r.norm_w != nullptr) {
     // the norm in front of the block (RouterParams): every CTA normalises the row for itself, CTA 0 publishes it
@@ -150,13 +149,10 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
     if (p.r.bias != nullptr) l = rn<T>(l + Elem<T>::to_float(reinterpret_cast<const T*>(p.r.bias)[e]));
     if (lane == 0) p.r.logits[e] = l;
   }
-  TOKEN_TRACE(1);
   bool alive = grid_barrier_bounded(p.gbar, p.wait_cycles, &s_flag, p.status);
-  TOKEN_TRACE(2);
 
   // ---- phase 1: every CTA selects the experts for itself; CTA 0 publishes ids, scores and the grouping ----
   if (alive) topk_softmax_tile<T, 1>(topk_args(p.r), 0, 1, &s_topk, s_ids, s_w, blockIdx.x == 0);
-  TOKEN_TRACE(9);
   if (warp == 0) {
     int n = 0;
     if (alive) {
@@ -191,7 +187,6 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
     if (lane == 0) s_nlive = n;
   }
   __syncthreads();
-  TOKEN_TRACE(11);
   if (alive && blockIdx.x == 0) {
     // The grouping tables of this one-token batch, for readers of the last call's grouping (what permute_block
     // leaves): the K pairs in expert order, every id valid and distinct because the top-k above produced them.
@@ -217,7 +212,6 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
     if (threadIdx.x == 0) *t.n_act = s_nlive;
   }
 
-  TOKEN_TRACE(3);
   // ---- phases 2 and 3 share one list of units and one ring per warp ----
   const int n_live = s_nlive;
   // warp-major: when the units do not divide evenly, the extra ones fall on ONE warp of many SMs, not on every warp of a few
@@ -336,9 +330,7 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
       reinterpret_cast<T*>(p.h)[(size_t)j * I + r0 + lane] = Elem<T>::from_float(__fmul_rn(sg, u));
     }
   }
-  TOKEN_TRACE(4);
   if (!grid_barrier_bounded(p.gbar, p.wait_cycles, &s_flag, p.status)) dead = true;     // h is complete
-  TOKEN_TRACE(5);
 
   for (; cu < total_units && !dead; cu += W) {
     const int r0 = (cu - U2) * 2;
@@ -414,7 +406,6 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
       reinterpret_cast<T*>(p.out)[r0 + lane] = Elem<T>::from_float(o);
     }
   }
-  TOKEN_TRACE(6);
   if (n_live == 0 && !dead) {
     // nothing served: the block contributes zeros
     for (int c = blockIdx.x * S::THREADS + threadIdx.x; c < H; c += (int)gridDim.x * S::THREADS) {
@@ -423,7 +414,6 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
       reinterpret_cast<T*>(p.out)[c] = Elem<T>::from_float(o);
     }
   }
-  TOKEN_TRACE(8);
   if (dead) {
     // A wait ran out.  Copies issued earlier may still be in flight towards this warp's ring: give each of them
     // a short, bounded chance to land before the shared memory can pass to another CTA.
