@@ -274,7 +274,7 @@ int b200moe_pack_int4(const void* w, int out_features, int in_features, int dtyp
 int b200moe_unpack_int4(const void* q, const void* scales, int out_features, int in_features, int dtype,
                         void* q_out, void* w_out, void* stream);
 
-/* Single-token batches (T = 1) of b200moe_forward_fused on a dense 16-bit model with ffn_kind AUTO run as ONE
+/* Batches of one or two tokens of b200moe_forward_fused / _fused_norm on a dense 16-bit model with ffn_kind AUTO run as ONE
  * cooperative launch that covers router, experts and combine (same results contract as the kernel chain; the
  * expert sums are taken in a different order, so outputs agree to rounding, routing bit for bit).  enable = 0
  * sends them through the kernel chain again (comparisons, per-kernel timing).  Default: enabled.  No counterpart
@@ -301,7 +301,7 @@ int b200moe_status(b200moe_ctx* ctx, int* device_status_out, void* stream);
 #define B200MOE_KERNEL_COMBINE 4
 #define B200MOE_KERNEL_EP_DISPATCH 5
 #define B200MOE_KERNEL_EP_RETURN 6
-#define B200MOE_KERNEL_TOKEN 7        /* the one-launch block of a single-token batch */
+#define B200MOE_KERNEL_TOKEN 7        /* the one-launch block of a batch of one or two tokens */
 #define B200MOE_KERNEL_CLASSES 8
 int b200moe_profile(b200moe_ctx* ctx, int enable);
 int b200moe_profile_read(b200moe_ctx* ctx, float* total_ms, int32_t* launches);

@@ -32,6 +32,7 @@
 #include "ffn_umma.cuh"
 #endif
 #include "moe_token.cuh"
+#include "moe_tokens.cuh"
 
 using namespace b200moe;
 
@@ -967,6 +968,73 @@ static int launch_token(b200moe_ctx* ctx, int layer, const void* x, int64_t* ids
   });
 }
 
+// Batches of two tokens of a dense 16-bit model through the fused entry: one cooperative launch (moe_tokens.cuh).
+// Same contract as launch_token.
+template <typename Tt, int NT>
+static int launch_tokens_nt(b200moe_ctx* ctx, const TokenParams& p, const SlotTable& tab, cudaStream_t st) {
+  const b200moe_config& c = ctx->cfg;
+  auto kn = moe_tokens_kernel<Tt, NT>;
+  static ConfiguredDevices configured, usable;   // per template instance
+  if (configured.needs(c.device)) {
+    int coop = 0, per_sm = 0;
+    cudaDeviceGetAttribute(&coop, cudaDevAttrCooperativeLaunch, c.device);
+    if (cudaFuncSetAttribute(kn, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)kTokensSmemBytes) == cudaSuccess &&
+        cudaOccupancyMaxActiveBlocksPerMultiprocessor(&per_sm, kn, TokensShape::THREADS, kTokensSmemBytes) == cudaSuccess && coop && per_sm >= 1)
+      usable.done(c.device);
+    cudaGetLastError();
+    configured.done(c.device);
+  }
+  if (usable.needs(c.device)) return B200MOE_E_UNSUPPORTED;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(ctx->sm_count);
+  cfg.blockDim = dim3(TokensShape::THREADS);
+  cfg.dynamicSmemBytes = kTokensSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeCooperative;     // every CTA resident: the grid barriers cannot starve
+  attr[0].val.cooperative = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  {
+    ProfScope prof(ctx, B200MOE_KERNEL_TOKEN, st);
+    cudaLaunchKernelEx(&cfg, kn, p, tab);
+  }
+  return post_launch(ctx, "moe_tokens_kernel");
+}
+
+static int launch_tokens(b200moe_ctx* ctx, int layer, const void* x, int T, int64_t* ids, void* scores, const void* residual, void* out,
+                         const PermuteParams& pp, const SlotTable& tab, const RouterNorm* norm, cudaStream_t st) {
+  const b200moe_config& c = ctx->cfg;
+  if (c.weight_mode != B200MOE_W_DENSE || c.act_dtype == B200MOE_F32) return B200MOE_E_UNSUPPORTED;
+  if (c.hidden_size % 8 || c.intermediate_size % 8) return B200MOE_E_UNSUPPORTED;
+  if (T != 2 || T * c.top_k > kTokensMaxPairs || (size_t)T * c.hidden_size * 2 > (size_t)kTokenMaxRowBytes ||
+      (size_t)T * c.top_k * c.intermediate_size * 2 > (size_t)kTokensMaxHBytes)
+    return B200MOE_E_UNSUPPORTED;
+  TokenParams p{};
+  p.r.x = x; p.r.wg = ctx->gate_w[layer]; p.r.bias = ctx->gate_bias[layer];
+  p.r.logits = ctx->logits; p.r.ids64 = ids; p.r.scores = scores;
+  p.r.T = T; p.r.H = c.hidden_size; p.r.E = c.num_experts; p.r.K = c.top_k;
+  p.r.perm = pp;
+  if (norm && norm->weight) {
+    if (c.hidden_size > kNormMaxChunks * kNormThreads * 8) return B200MOE_E_UNSUPPORTED;
+    p.r.norm_res = norm->residual; p.r.norm_w = norm->weight; p.r.norm_eps = norm->eps;
+    p.r.normed_out = norm->normed_out; p.r.res_out = norm->res_out;
+  }
+  p.experts = ctx->d_experts + (size_t)layer * c.num_experts;
+  p.h = ctx->h; p.residual = residual; p.out = out; p.I = c.intermediate_size;
+  p.gbar = ctx->tile_counter + c.max_tokens + 1;
+  p.status = ctx->status;
+  p.wait_cycles = 1ll << 31;
+  return dispatch_dtype(ctx, c.act_dtype, [&](auto tag) -> int {
+    using Tt = decltype(tag);
+    if constexpr (sizeof(Tt) != 2) {
+      return B200MOE_E_UNSUPPORTED;
+    } else {
+      return launch_tokens_nt<Tt, 2>(ctx, p, tab, st);
+    }
+  });
+}
+
 // route_first: the ids / scores buffers are OUTPUTS of the router, which this call launches first (fused entry).
 static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const int64_t* ids, const void* scores,
                        int scores_dtype, const int32_t* expert_slot, const int32_t* order, const void* residual,
@@ -995,6 +1063,10 @@ static int run_experts(b200moe_ctx* ctx, int layer, const void* x, int T, const 
   pp.act_list = ctx->act_list; pp.n_act = ctx->n_act; pp.status = ctx->status;
   if (route_first && T == 1 && ffn_kind == B200MOE_FFN_AUTO && ctx->token_kernel) {
     rc = launch_token(ctx, layer, route_x ? route_x : x, const_cast<int64_t*>(ids), const_cast<void*>(scores), residual, out, pp, tab, norm, st);
+    if (rc != B200MOE_E_UNSUPPORTED) return rc;
+  }
+  if (route_first && T == 2 && !order && !expert_slot && ffn_kind == B200MOE_FFN_AUTO && ctx->token_kernel) {
+    rc = launch_tokens(ctx, layer, route_x ? route_x : x, T, const_cast<int64_t*>(ids), const_cast<void*>(scores), residual, out, pp, tab, norm, st);
     if (rc != B200MOE_E_UNSUPPORTED) return rc;
   }
   const bool fused_grouping = route_first && T * c.top_k <= kFusePermuteMaxPairs;

@@ -216,8 +216,8 @@ __device__ __forceinline__ TopkArgs topk_args(const RouterParams& p) {
   return TopkArgs{p.logits_in, p.logits, p.ids64, p.scores, p.bitmap, p.E, p.K};
 }
 
-// ids_s / w_s (shared memory, K entries; the score as the model dtype holds it) receive a private copy of token
-// t0's routing for a caller that goes on to use it; write_global = false leaves ids / scores / bitmap untouched.
+// ids_s / w_s (shared memory, ntok * K entries; the score as the model dtype holds it) receive a private copy of the
+// routing for a caller that goes on to use it; write_global = false leaves ids / scores / bitmap untouched.
 template <typename T, int TT>
 __device__ __noinline__ void topk_softmax_tile(TopkArgs a, int t0, int ntok, TopkSmem<TT>* sm, int* ids_s, float* w_s, bool write_global) {
   static_assert(TT <= kRouterThreads / 32, "one warp per token in the last step");
@@ -313,7 +313,7 @@ __device__ __noinline__ void topk_softmax_tile(TopkArgs a, int t0, int ntok, Top
       reinterpret_cast<T*>(a.scores)[at] = Elem<T>::from_float(sc);
       if (a.bitmap != nullptr) atomicOr(a.bitmap + (idx >> 6), 1ull << (idx & 63));
     }
-    if (ids_s != nullptr && tt == 0) { ids_s[lane] = idx; w_s[lane] = rn<T>(sc); }
+    if (ids_s != nullptr) { ids_s[tt * K + lane] = idx; w_s[tt * K + lane] = rn<T>(sc); }
   }
 }
 

@@ -1,5 +1,5 @@
-"""GPU: the one-launch block of a single-token batch (router, experts and combine in one cooperative kernel)
-against the oracle and against the kernel chain it replaces, through the C ABI."""
+"""GPU: the one-launch block of batches of one and two tokens (router, experts and combine in one cooperative
+kernel) against the oracle and against the kernel chain it replaces, through the C ABI."""
 import pytest
 import torch
 
@@ -52,26 +52,30 @@ def _check_close(got, want, dtype):
     assert O.mean_rel(got, want) <= tol_r
 
 
-# (H, E, K, I): Qwen3-like rows (down projection in four-row units), a long-I shape (down projection in K
-# quarters, as the Mixtral-shaped layer takes it), a shape whose rows are ragged against the 2 KB ring segments
-SHAPES = [(2048, 128, 8, 768), (512, 8, 2, 4096), (1032, 16, 4, 520)]
+# (H, E, K, I): Qwen3-like rows, a long-I shape (down_proj rows of several ring segments, as the Mixtral-shaped layer
+# has them), a shape whose rows are ragged against the
+# ring segments
+SHAPES = [(2048, 128, 8, 768), (512, 8, 2, 3072), (1032, 16, 4, 520)]
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
 @pytest.mark.parametrize("shape", SHAPES)
-def test_token_block_matches_oracle_and_chain(shape, dtype):
+@pytest.mark.parametrize("T", [1, 2])
+def test_token_block_matches_oracle_and_chain(shape, dtype, T):
     H, E, K, I = shape
     gate_w, experts = _layer(H, E, K, I, dtype, seed=H + E)
     ctx = _ctx(H, E, K, I, dtype, gate_w, experts)
-    g = torch.Generator().manual_seed(7)
-    for trial in range(4):
-        x = torch.randn(1, H, generator=g).to(dtype)
-        res = torch.randn(1, H, generator=g).to(dtype) if trial % 2 else None
+    g = torch.Generator().manual_seed(7 + T)
+    for trial in range(3):
+        x = torch.randn(T, H, generator=g).to(dtype)
+        if trial == 2 and T > 1:
+            x[1] = x[0]                                              # two tokens with the same routing: experts with two rows
+        res = torch.randn(T, H, generator=g).to(dtype) if trial % 2 else None
         xd, rd = x.cuda(), (None if res is None else res.cuda())
         seen = _launches(ctx, lambda: ctx.forward_fused(0, xd, residual=rd))
         assert seen == {"token_block": 1}, seen                      # the one-launch path is the one that ran
         out, ids, scores = ctx.forward_fused(0, xd, residual=rd, return_routing=True)
-        tables = ctx.last_tables(1)
+        tables = ctx.last_tables(T)
         assert ctx.status() == 0
         want_ids, want_scores, _ = O.route(x, gate_w, K)
         assert torch.equal(ids.cpu(), want_ids) and torch.equal(scores.cpu(), want_scores)       # bit-exact routing
@@ -82,7 +86,7 @@ def test_token_block_matches_oracle_and_chain(shape, dtype):
         seen = _launches(ctx, lambda: ctx.forward_fused(0, xd, residual=rd))
         assert "token_block" not in seen
         out2, ids2, scores2 = ctx.forward_fused(0, xd, residual=rd, return_routing=True)
-        tables2 = ctx.last_tables(1)
+        tables2 = ctx.last_tables(T)
         ctx.set_token_kernel(True)
         assert torch.equal(ids, ids2) and torch.equal(scores, scores2)
         for a, b in zip(tables, tables2):
@@ -99,8 +103,8 @@ def test_token_block_skips_unserved_experts_and_adds_bias():
     ctx = _ctx(H, E, K, I, dtype, gate_w, experts, bias=bias)
     g = torch.Generator().manual_seed(11)
     hit_unserved = 0
-    for _ in range(8):
-        x = torch.randn(1, H, generator=g).to(dtype)
+    for trial in range(8):
+        x = torch.randn(1 + trial % 2, H, generator=g).to(dtype)
         out, ids, scores = ctx.forward_fused(0, x.cuda(), return_routing=True)
         assert ctx.status() == 0
         want_ids, want_scores, _ = O.route(x, gate_w, K, bias=bias)
@@ -119,7 +123,7 @@ def test_token_block_many_calls_and_graph_replay():
     gate_w, experts = _layer(H, E, K, I, dtype, seed=21)
     ctx = _ctx(H, E, K, I, dtype, gate_w, experts)
     g = torch.Generator().manual_seed(5)
-    xs = [torch.randn(1, H, generator=g).to(dtype).cuda() for _ in range(4)]
+    xs = [torch.randn(1 + i % 2, H, generator=g).to(dtype).cuda() for i in range(4)]
     first = [ctx.forward_fused(0, x).clone() for x in xs]
     for _ in range(100):
         for x, want in zip(xs, first):
@@ -161,4 +165,5 @@ def test_other_shapes_keep_the_chain():
     xb = x.to(torch.bfloat16).cuda()
     assert "token_block" not in _launches(ctx, lambda: ctx.forward_fused(0, xb, ffn_kind=FFN_GEMV))
     assert _launches(ctx, lambda: ctx.forward_fused(0, xb)) == {"token_block": 1}
-    assert "token_block" not in _launches(ctx, lambda: ctx.forward_fused(0, xb.repeat(2, 1)))
+    assert _launches(ctx, lambda: ctx.forward_fused(0, xb.repeat(2, 1))) == {"token_block": 1}
+    assert "token_block" not in _launches(ctx, lambda: ctx.forward_fused(0, xb.repeat(3, 1)))
