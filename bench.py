@@ -362,8 +362,11 @@ def per_batch_table(w: Workload, peak: float):
 
 def roofline_record(w: Workload, prof, ms_per_step, peak, peak_kind):
     """Roofline of the dominant kernel (gate/up weight streaming): bytes per launch / mean launch time."""
-    # a single-token batch that ran as the one-launch block has no gate/up launch of its own
-    gu_batches = [T for T in w.batches if not (T == 1 and prof.get("token_block", (0.0, 0))[1])] or list(w.batches)
+    # a batch that ran as the one-launch block has no gate/up launch of its own: every batch of a sweep gives
+    # exactly one launch of either kind, and the one-launch block takes the smallest batches
+    tb_n, gu_n0 = prof.get("token_block", (0.0, 0))[1], prof["ffn_gate_up"][1]
+    n_tok = round(len(w.batches) * tb_n / (tb_n + gu_n0)) if (tb_n + gu_n0) else 0
+    gu_batches = sorted(w.batches)[n_tok:] or list(w.batches)
     gu_bytes = sum(algorithmic_bytes(w.H, w.E, w.I, T, w.n_active[T], w.int4)[1] for T in gu_batches) / len(gu_batches)
     layer_bytes = sum(algorithmic_bytes(w.H, w.E, w.I, T, w.n_active[T], w.int4)[0] for T in w.batches)
     gu_ms, gu_n = prof["ffn_gate_up"]
