@@ -4,8 +4,10 @@
 // (demo/src/layers/moe_layer.py:25-60, demo/src/layers/mlp.py:209-231, demo/src/model/qwen3_runner.py:352-383)
 // for the smallest verify batch.  The token tile NT is a template parameter and the kernel is correct for up to
 // four tokens, but only two are dispatched here: on the Qwen3-shaped layer two tokens take 47 us against 54 us for
-// the kernel chain, four tokens 88 us against 75 us (a down unit then walks ~29 experts, one ring stage after the
-// other, and the tensor-core chain's fixed cost is spread over four tokens).
+// the kernel chain, four tokens 88 us against 75 us: global-timer marks put the gate/up phase at 5.8 TB/s but the
+// down phase at 2.8 TB/s - a down unit walks ~30 experts, one 6 KB ring stage after the other (2.2 us per stage, of
+// which the sixteen warp reductions and the combine arithmetic of every expert pair are about half), and only
+// 1024 of the 1184 warps have a unit.
 //
 // What differs from the single-token kernel:
 //  * the (token, expert) pairs - at most 32, one lane each - are grouped by expert in every CTA by counting
