@@ -56,12 +56,12 @@ def test_rmsnorm_module_matches_oracle(T, H):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-@pytest.mark.parametrize("T", [1, 5, 16, 17, 40])
+@pytest.mark.parametrize("T", [1, 5, 32, 33, 40])
 @pytest.mark.parametrize("with_residual", [True, False])
 def test_norm_fused_into_the_router_equals_norm_then_block(dtype, T, with_residual):
     """b200moe_forward_fused_norm (the norm applied inside the router kernel's load of the tokens) against the
     two-step form b200moe_rmsnorm -> b200moe_forward_fused: normalised rows, new residual, ids and output all
-    bit-identical, for the single-token-per-CTA router (T <= 16) and the tile router (T > 16)."""
+    bit-identical, for the single-token-per-CTA router (T <= 32) and the tile router (T > 32)."""
     from on_device_sd_b200 import MoEContext
     from on_device_sd_b200.synth import make_layer
     H, E, K, I = 256, 16, 4, 128

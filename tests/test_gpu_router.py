@@ -158,3 +158,26 @@ def test_router_empty_batch_and_errors():
     # all-zero logits: ids follow torch's tie order, scores are uniform
     ids, scores = ctx.route(0, torch.zeros(2, 64, dtype=torch.bfloat16, device="cuda"))
     assert ids.cpu().tolist() == [[1, 0], [1, 0]] and torch.equal(scores.float().cpu(), torch.full((2, 2), 0.5))
+
+
+@pytest.mark.parametrize("T", [1, 2, 8, 32, 40])
+@pytest.mark.parametrize("E,K,groups", [(128, 8, 16), (8, 2, 3), (60, 4, 60), (256, 32, 40)])
+def test_tied_logits_follow_torch_order_in_every_router_form(T, E, K, groups):
+    """Gate rows repeated in groups give exactly equal logits, so the kept set and its order are decided by the tie
+    rules alone (lowest index first into the set, then the 32-slot network's permutation).  The batch sizes reach
+    the one-launch block (T = 1, 2: routing read back from the fused entry), the one-token-per-CTA router (CTA-wide
+    counting top-k) and the token-tile router (one warp per token); all must give the oracle's torch-CUDA order."""
+    H, I = 256, 128
+    g = torch.Generator().manual_seed(E + K + T)
+    base = (torch.randn(groups, H, generator=g) * 0.05).to(torch.bfloat16)
+    gate_w = base[torch.arange(E) % groups].contiguous()
+    x = torch.randn(T, H, generator=g).to(torch.bfloat16)
+    ctx = _ctx(H, E, K, I, torch.bfloat16, max_tokens=64)
+    ctx.set_gate(0, gate_w.cuda())
+    want_ids, want_scores, _ = O.route(x, gate_w, K)
+    ids, scores = ctx.route(0, x.cuda())
+    assert torch.equal(ids.cpu(), want_ids) and torch.equal(scores.cpu(), want_scores)
+    # the fused entry (no experts registered: the block contributes zeros) routes through the one-launch kernels for T <= 2
+    out, ids2, scores2 = ctx.forward_fused(0, x.cuda(), return_routing=True)
+    assert torch.equal(ids2.cpu(), want_ids) and torch.equal(scores2.cpu(), want_scores)
+    assert ctx.status() == 0 and float(out.abs().max()) == 0.0
