@@ -63,6 +63,47 @@ __device__ __forceinline__ bool grid_barrier_bounded(unsigned* bar, long long li
 }
 
 
+// One warp: the gate logit of expert row `wrow` for the token row `xr` (shared memory), with router_kernel's
+// certificate - four fp32 accumulators per lane, eight chunk positions per trip, sum|x w| beside them; a result
+// closer to a rounding boundary of T than the bound on the fp32 summation error is recomputed with fp64
+// accumulation.  Returns the logit rounded to T (bias added in T), the same value in every lane.
+template <typename T>
+__device__ __forceinline__ float token_gate_logit(const unsigned char* xr, const T* wrow, const T* bias, int e, int H, int lane) {
+  constexpr int CB = 8 * (int)sizeof(T);
+  const int nch = H / 8;
+  float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+  float sabs = 0.0f;
+  for (int c0 = lane; c0 < nch; c0 += 32 * 8) {
+    Chunk<T> wc[8];
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (c0 + 32 * u < nch) wc[u].template load<false>(wrow + (size_t)(c0 + 32 * u) * 8);
+      else wc[u].zero();
+    }
+#pragma unroll
+    for (int u = 0; u < 8; ++u) {
+      if (c0 + 32 * u >= nch) break;
+      Chunk<T> xc;
+      xc.from_smem(xr + (size_t)(c0 + 32 * u) * CB);
+      float wf[8], xf[8];
+      wc[u].unpack(wf);
+      xc.unpack(xf);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        acc[i & 3] = fmaf(xf[i], wf[i], acc[i & 3]);
+        sabs = fmaf(fabsf(xf[i]), fabsf(wf[i]), sabs);
+      }
+    }
+  }
+  const float cH = (float)(H / 128 + 12) * 5.9604645e-8f * 1.01f;
+  float s = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
+  const float bound = cH * warp_sum(sabs) + 1e-37f;
+  if (!(boundary_distance<T>(s) > bound)) s = (float)exact_dot<T, true>(reinterpret_cast<const T*>(xr), wrow, nch, lane);
+  float l = rn<T>(s);
+  if (bias != nullptr) l = rn<T>(l + Elem<T>::to_float(bias[e]));
+  return l;
+}
+
 constexpr int kTokenMaxRowBytes = 16384;   // the token row kept in shared memory beside the rings
 
 template <typename S> constexpr size_t token_smem_bytes() { return S::SMEM + kTokenMaxRowBytes; }
@@ -115,38 +156,7 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
   __syncthreads();
 
   for (int e = blockIdx.x + (int)gridDim.x * warp; e < E; e += (int)gridDim.x * S::WARPS) {
-    // the certificate of router_kernel: four fp32 accumulators per lane, eight chunk positions per trip
-    const T* wrow = reinterpret_cast<const T*>(p.r.wg) + (size_t)e * H;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    float sabs = 0.0f;
-    for (int c0 = lane; c0 < nch; c0 += 32 * 8) {
-      Chunk<T> wc[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (c0 + 32 * u < nch) wc[u].template load<false>(wrow + (size_t)(c0 + 32 * u) * 8);
-        else wc[u].zero();
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (c0 + 32 * u >= nch) break;
-        Chunk<T> xc;
-        xc.from_smem(xrow + (size_t)(c0 + 32 * u) * CB);
-        float wf[8], xf[8];
-        wc[u].unpack(wf);
-        xc.unpack(xf);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          acc[i & 3] = fmaf(xf[i], wf[i], acc[i & 3]);
-          sabs = fmaf(fabsf(xf[i]), fabsf(wf[i]), sabs);
-        }
-      }
-    }
-    const float cH = (float)(H / 128 + 12) * 5.9604645e-8f * 1.01f;
-    float s = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
-    const float bound = cH * warp_sum(sabs) + 1e-37f;
-    if (!(boundary_distance<T>(s) > bound)) s = (float)exact_dot<T, true>(reinterpret_cast<const T*>(xrow), wrow, nch, lane);
-    float l = rn<T>(s);
-    if (p.r.bias != nullptr) l = rn<T>(l + Elem<T>::to_float(reinterpret_cast<const T*>(p.r.bias)[e]));
+    const float l = token_gate_logit<T>(xrow, reinterpret_cast<const T*>(p.r.wg) + (size_t)e * H, reinterpret_cast<const T*>(p.r.bias), e, H, lane);
     if (lane == 0) p.r.logits[e] = l;
   }
   bool alive = grid_barrier_bounded(p.gbar, p.wait_cycles, &s_flag, p.status);
@@ -217,14 +227,27 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
   // warp-major: when the units do not divide evenly, the extra ones fall on ONE warp of many SMs, not on every warp of a few
   const int gw = warp * (int)gridDim.x + blockIdx.x;
   const int W = gridDim.x * S::WARPS;
-  const int half_I = I / 2;
-  const int U2 = n_live * half_I;                       // gate/up: rows (r, r+1) of gate_proj and of up_proj of one expert
+  const int rb2 = H * (int)sizeof(T);
+  // gate/up units: rows (r, r+1) of gate_proj and of up_proj of one expert - or, when that leaves the warps with
+  // noticeably unequal shares (Mixtral shape: 14336 units on 1184 warps, one warp in nine holds a thirteenth), row r
+  // of both matrices with every row cut in two halves along K, which makes twice as many units of half the size
+  bool halfrow = false;
+  if (n_live > 0 && (rb2 / 2) % SEG == 0) {
+    // rounds * W / units is a warp's largest share over the mean; halves are taken when they bring it down by 0.02:
+    // rounds_half * W / (2u) + 0.02 < rounds_full * W / u, in integers
+    const long long u_full = (long long)n_live * (I / 2);
+    const long long rounds_full = (u_full + W - 1) / W, rounds_half = (2 * u_full + W - 1) / W;
+    halfrow = 25 * rounds_half * W + u_full < 50 * rounds_full * W;
+  }
+  const int upe = halfrow ? I : I / 2;                   // units per expert
+  const int U2 = n_live * upe;
+  const int rb2u = halfrow ? rb2 / 2 : rb2;               // bytes one stream of a gate/up unit covers
   // down projection + combine: rows (r, r+1) of down_proj of EVERY live expert, two experts per stage in the
   // combine's accumulation order, so that the warp holding a row's K products also adds them up
   const int U3 = n_live > 0 ? H / 2 : 0;
   const int npair = (n_live + 1) / 2;
   const int total_units = U2 + U3;
-  const int rb2 = H * (int)sizeof(T), nseg2 = (rb2 + SEG - 1) / SEG;
+  const int nseg2 = (rb2u + SEG - 1) / SEG;
   const int rb3 = I * (int)sizeof(T), nseg3 = (rb3 + SEG - 1) / SEG;
   const uint64_t policy = l2_policy_evict_first();
   const int sidx4 = lane & 3;
@@ -236,8 +259,10 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
   int p_nstage = 0;
   auto open_unit = [&](int u) {
     if (u < U2) {
-      const int j = u / half_I, r0 = (u - j * half_I) * 2;
-      prow = s_wp[sidx4 >> 1][j] + (size_t)(r0 + (sidx4 & 1)) * rb2;
+      const int j = u / upe, g = u - j * upe;
+      // streams: (gate r, gate r+1, up r, up r+1), or (gate r first half, second half, up r first half, second half)
+      prow = halfrow ? s_wp[sidx4 >> 1][j] + (size_t)g * rb2 + (size_t)(sidx4 & 1) * rb2u
+                     : s_wp[sidx4 >> 1][j] + (size_t)(2 * g + (sidx4 & 1)) * rb2;
       p_nstage = nseg2;
     } else {
       p_row3 = (u - U2) * 2 + (sidx4 & 1);
@@ -252,7 +277,7 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
     uint32_t bytes, streams = 4;
     bool mine = true;
     if (pu < U2) {
-      bytes = (uint32_t)min(SEG, rb2 - ps * SEG);
+      bytes = (uint32_t)min(SEG, rb2u - ps * SEG);
       src = prow + (size_t)ps * SEG;
     } else {
       const int q = ps / nseg3, seg = ps - q * nseg3;
@@ -296,38 +321,52 @@ __global__ void __launch_bounds__(S::THREADS, 1) moe_token_kernel(TokenParams p,
 
   int cu = gw;
   for (; cu < U2 && !dead; cu += W) {
-    const int j = cu / half_I, r0 = (cu - j * half_I) * 2;
+    const int j = cu / upe, g = cu - j * upe;
     float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
     for (int seg = 0; seg < nseg2; ++seg) {
       const unsigned char* sbase = next_stage();
       if (sbase == nullptr) break;
-      const int nchunk = min(SEG, rb2 - seg * SEG) / CB;
+      const int nchunk = min(SEG, rb2u - seg * SEG) / CB;
       for (int cl = lane; cl < nchunk; cl += 32) {
         Chunk<T> xc;
+        float xf[2][8];
         xc.from_smem(xrow + (size_t)seg * SEG + (size_t)cl * CB);
-        float xf[8];
-        xc.unpack(xf);
+        xc.unpack(xf[0]);
+        if (halfrow) {                    // the odd streams hold the second half of the row
+          xc.from_smem(xrow + (size_t)rb2u + (size_t)seg * SEG + (size_t)cl * CB);
+          xc.unpack(xf[1]);
+        }
 #pragma unroll
         for (int s = 0; s < 4; ++s) {
           Chunk<T> wc;
           wc.from_smem(sbase + (size_t)s * SEG + (size_t)cl * CB);
           float wf[8];
           wc.unpack(wf);
+          const float* xs = (halfrow && (s & 1)) ? xf[1] : xf[0];
 #pragma unroll
-          for (int i = 0; i < 8; ++i) acc[s] = fmaf(wf[i], xf[i], acc[s]);
+          for (int i = 0; i < 8; ++i) acc[s] = fmaf(wf[i], xs[i], acc[s]);
         }
       }
       __syncwarp();   // every lane is done with the slot before it is refilled
     }
     if (dead) break;
+    // rounding points of the reference's SwiGLU
+    if (halfrow) {
+      const float gs = warp_sum(acc[0] + acc[1]), us = warp_sum(acc[2] + acc[3]);
+      if (lane == 0) {
+        const float gg = rn<T>(gs), uu = rn<T>(us);
+        const float sg = rn<T>(silu_f32(gg));
+        reinterpret_cast<T*>(p.h)[(size_t)j * I + g] = Elem<T>::from_float(__fmul_rn(sg, uu));
+      }
+    } else {
 #pragma unroll
-    for (int s = 0; s < 4; ++s) acc[s] = warp_sum(acc[s]);
-    if (lane < 2) {
-      // stream order is (gate r, gate r+1, up r, up r+1); rounding points of the reference's SwiGLU
-      const float g = rn<T>(lane == 0 ? acc[0] : acc[1]);
-      const float u = rn<T>(lane == 0 ? acc[2] : acc[3]);
-      const float sg = rn<T>(silu_f32(g));
-      reinterpret_cast<T*>(p.h)[(size_t)j * I + r0 + lane] = Elem<T>::from_float(__fmul_rn(sg, u));
+      for (int s = 0; s < 4; ++s) acc[s] = warp_sum(acc[s]);
+      if (lane < 2) {
+        const float gg = rn<T>(lane == 0 ? acc[0] : acc[1]);
+        const float uu = rn<T>(lane == 0 ? acc[2] : acc[3]);
+        const float sg = rn<T>(silu_f32(gg));
+        reinterpret_cast<T*>(p.h)[(size_t)j * I + 2 * g + lane] = Elem<T>::from_float(__fmul_rn(sg, uu));
+      }
     }
   }
   if (!grid_barrier_bounded(p.gbar, p.wait_cycles, &s_flag, p.status)) dead = true;     // h is complete

@@ -89,40 +89,9 @@ __global__ void __launch_bounds__(TokensShape::THREADS, 1) moe_tokens_kernel(Tok
   __syncthreads();
 
   for (int it = blockIdx.x + (int)gridDim.x * warp; it < nt * E; it += (int)gridDim.x * S::WARPS) {
-    // the certificate of router_kernel: four fp32 accumulators per lane, eight chunk positions per trip
     const int t = it / E, e = it - t * E;
-    const T* wrow = reinterpret_cast<const T*>(p.r.wg) + (size_t)e * H;
-    const unsigned char* xr = xrows + (size_t)t * xrow_bytes;
-    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-    float sabs = 0.0f;
-    for (int c0 = lane; c0 < nch; c0 += 32 * 8) {
-      Chunk<T> wc[8];
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (c0 + 32 * u < nch) wc[u].template load<false>(wrow + (size_t)(c0 + 32 * u) * 8);
-        else wc[u].zero();
-      }
-#pragma unroll
-      for (int u = 0; u < 8; ++u) {
-        if (c0 + 32 * u >= nch) break;
-        Chunk<T> xc;
-        xc.from_smem(xr + (size_t)(c0 + 32 * u) * CB);
-        float wf[8], xf[8];
-        wc[u].unpack(wf);
-        xc.unpack(xf);
-#pragma unroll
-        for (int i = 0; i < 8; ++i) {
-          acc[i & 3] = fmaf(xf[i], wf[i], acc[i & 3]);
-          sabs = fmaf(fabsf(xf[i]), fabsf(wf[i]), sabs);
-        }
-      }
-    }
-    const float cH = (float)(H / 128 + 12) * 5.9604645e-8f * 1.01f;
-    float s = warp_sum((acc[0] + acc[1]) + (acc[2] + acc[3]));
-    const float bound = cH * warp_sum(sabs) + 1e-37f;
-    if (!(boundary_distance<T>(s) > bound)) s = (float)exact_dot<T, true>(reinterpret_cast<const T*>(xr), wrow, nch, lane);
-    float l = rn<T>(s);
-    if (p.r.bias != nullptr) l = rn<T>(l + Elem<T>::to_float(reinterpret_cast<const T*>(p.r.bias)[e]));
+    const float l = token_gate_logit<T>(xrows + (size_t)t * xrow_bytes, reinterpret_cast<const T*>(p.r.wg) + (size_t)e * H,
+                                        reinterpret_cast<const T*>(p.r.bias), e, H, lane);
     if (lane == 0) p.r.logits[(size_t)t * E + e] = l;
   }
   bool alive = grid_barrier_bounded(p.gbar, p.wait_cycles, &s_flag, p.status);

@@ -55,7 +55,8 @@ def _check_close(got, want, dtype):
 # (H, E, K, I): Qwen3-like rows, a long-I shape (down_proj rows of several ring segments, as the Mixtral-shaped layer
 # has them), a shape whose rows are ragged against the
 # ring segments
-SHAPES = [(2048, 128, 8, 768), (512, 8, 2, 3072), (1032, 16, 4, 520)]
+# and a shape whose gate/up units the single-token kernel cuts in two along K to balance the warps
+SHAPES = [(2048, 128, 8, 768), (512, 8, 2, 3072), (1032, 16, 4, 520), (4096, 8, 2, 1536)]
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
