@@ -167,10 +167,6 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
   const int tiles = (Rdim + TILE_ROWS - 1) / TILE_ROWS;
   const int sgroups = Kdim / 128;
 
-  if (DUAL) pdl_wait();                          // the token copy of the gather kernel must be complete
-  pdl_trigger();
-  const int total = (*p.n_act) * tiles;
-
   if (threadIdx.x == 0) {
     for (int i = 0; i < WSTAGES; ++i) { mbar_init(&w_full[i], 1); mbar_init(&w_empty[i], 4); }
     for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 4); mbar_init(&empty[i], 1); }
@@ -188,6 +184,11 @@ __global__ void __launch_bounds__(kI4uThreads, 1) ffn_int4_umma_kernel(const __g
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // the token copy of the gather kernel (and the tables before it) must be complete: gate/up waits here, with its
+  // barriers and its tensor memory set up while the predecessor was still running
+  if (DUAL) pdl_wait();
+  pdl_trigger();
+  const int total = (*p.n_act) * tiles;
 
   if (warp == 0) {
     // ------------------------------ TMA producer: packed weight tiles (whole warp, one elected lane issues) ------------------------------

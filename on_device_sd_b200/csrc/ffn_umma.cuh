@@ -172,13 +172,7 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   const int nkb = (Kdim + kUmmaBK - 1) / kUmmaBK;
   const int tiles = (Rdim + TILE_ROWS - 1) / TILE_ROWS;
 
-  // Gate/up follows the permute kernel directly and needs its tables at once.  The down
-  // projection follows gate/up: the tables were complete before gate/up could start, so its
-  // weight stream starts immediately and only the loaders (readers of h) wait for gate/up to finish.
-  if (DUAL) pdl_wait();
-  pdl_trigger();
   const int KS = DUAL ? 1 : up.ksplit;
-  const int total = (*p.n_act) * tiles * KS;
   // work item -> (expert slot in act_list, row tile, K slice); k-blocks [kb0, kb1) of the slice
 #define B200MOE_DECODE_ITEM(item)                                   \
   const int ks_ = (item) % KS;                                      \
@@ -202,6 +196,13 @@ __global__ void __launch_bounds__(kUmmaThreads, 1) ffn_umma_kernel(UmmaParams up
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_holder;
+  // Gate/up follows the router / permute kernel directly and needs its tables: it waits here, with its barriers
+  // and its tensor memory already set up while the predecessor was still running.  The down projection follows
+  // gate/up: the tables were complete before gate/up could start, so its weight stream starts immediately and
+  // only the loaders (readers of h) wait for gate/up to finish.
+  if (DUAL) pdl_wait();
+  pdl_trigger();
+  const int total = (*p.n_act) * tiles * KS;
 
   if (warp == 0) {
     // ------------------------------ TMA producer ------------------------------
