@@ -56,7 +56,7 @@ def test_rmsnorm_module_matches_oracle(T, H):
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
-@pytest.mark.parametrize("T", [1, 5, 32, 33, 40])
+@pytest.mark.parametrize("T", [1, 2, 5, 32, 33, 40])
 @pytest.mark.parametrize("with_residual", [True, False])
 def test_norm_fused_into_the_router_equals_norm_then_block(dtype, T, with_residual):
     """b200moe_forward_fused_norm (the norm applied inside the router kernel's load of the tokens) against the
